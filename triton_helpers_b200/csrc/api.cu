@@ -1,0 +1,31 @@
+// Library-wide entry points: version, error text, cached device attributes.
+#include "common.cuh"
+
+#include <mutex>
+
+namespace th {
+
+char *last_error_buffer() {
+    static thread_local char buffer[kErrorBufferBytes] = "";
+    return buffer;
+}
+
+int sm_count() {
+    static std::mutex guard;
+    static int cache[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    std::lock_guard<std::mutex> lock(guard);
+    if (cache[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cache[dev] = n;
+    }
+    return cache[dev];
+}
+
+}  // namespace th
+
+extern "C" int th_version(void) { return 1; }
+
+extern "C" const char *th_last_error_string(void) { return th::last_error_buffer(); }

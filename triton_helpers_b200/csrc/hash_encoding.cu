@@ -1,0 +1,643 @@
+// Multiresolution hash encoding for sm_100a: forward gather/interpolate and backward
+// scatter-add.  Replaces the Triton kernels of
+// triton_helpers/layers/hash_encoding/kernel.py:175-306 (_fwd_kernel) and :322-440 (_bwd_kernel);
+// the index and weight arithmetic follows that file's CPU path (:443-479), which is the
+// parity contract:
+//   cell   = floor(x * res)                 one float32 multiply per level, no FMA contraction
+//   dense  : index = sum_d corner_d * res^d
+//   hashed : index = xor_d(corner_d * prime_d) mod rows
+//   t      = x * res - cell ;  weight(corner) = prod_d (bit_d ? t_d : 1 - t_d), axis order 0,1,2
+//
+// Work decomposition: one thread per point, 256 points per CTA.  The CTA stages its
+// coordinates through shared memory with 128-bit coalesced loads; each thread then walks
+// the levels in register groups of LG levels, so the LG * 2^D row gathers of a group are
+// all in flight together, and writes (forward) or reads (backward) its slice of the
+// [N, L*F] matrix with 128-bit accesses.  Tables are read through the read-only path and
+// are meant to stay L2 resident; outputs and incoming gradients are streamed.
+//
+// Backward contention: lanes of a warp that fall in the same cell of a level are found
+// with one match.any per level; their contributions are summed in registers and the first
+// lane of each group issues a single vector red.global.add per corner, so a cluster of
+// points costs one memory atomic per corner instead of one per point.
+#include "common.cuh"
+
+namespace th {
+namespace {
+
+constexpr int kThreads = 256;
+
+struct LevelParams {
+    uint32_t res[TH_MAX_LEVELS];
+    uint32_t rows[TH_MAX_LEVELS];
+    unsigned long long offset[TH_MAX_LEVELS];  // first row of the level
+    uint32_t primes[TH_MAX_DIMS];
+    uint32_t hashed_mask;  // bit l: level l uses the spatial hash
+    uint32_t pow2_mask;    // bit l: rows[l] is a power of two
+    float scale;
+};
+
+struct CoordView {
+    const void *ptr;
+    long long stride_n, stride_d;  // in elements
+    int dtype;
+    int packed_f32;  // float32, contiguous (stride_d == 1, stride_n == D) and 16-byte aligned
+};
+
+// ---- coordinates ----------------------------------------------------------------------------
+
+template <int D>
+__device__ __forceinline__ void load_coords_strided(const CoordView &cv, long long i, float (&x)[D]) {
+#pragma unroll
+    for (int d = 0; d < D; ++d) {
+        const long long e = i * cv.stride_n + d * cv.stride_d;
+        if (cv.dtype == TH_F32) {
+            x[d] = __ldcs(static_cast<const float *>(cv.ptr) + e);
+        } else if (cv.dtype == TH_F16) {
+            x[d] = __half2float(static_cast<const __half *>(cv.ptr)[e]);
+        } else {
+            x[d] = __bfloat162float(static_cast<const __nv_bfloat16 *>(cv.ptr)[e]);
+        }
+    }
+}
+
+// The CTA's 256 * D floats are contiguous: fetch them as float4, then each thread picks its D values.
+template <int D>
+__device__ __forceinline__ bool load_coords(const CoordView &cv, long long n_points, float (&x)[D], float *stage) {
+    const long long i = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
+    if (cv.packed_f32) {
+        const long long first = static_cast<long long>(blockIdx.x) * kThreads * D;  // multiple of 4
+        const long long total = n_points * D;
+        const float *src = static_cast<const float *>(cv.ptr);
+        for (int v = threadIdx.x; v < kThreads * D / 4; v += kThreads) {
+            const long long e = first + 4ll * v;
+            if (e + 3 < total) {
+                reinterpret_cast<float4 *>(stage)[v] = __ldcs(reinterpret_cast<const float4 *>(src + e));
+            } else {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) stage[4 * v + k] = (e + k < total) ? src[e + k] : 0.f;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int d = 0; d < D; ++d) x[d] = stage[threadIdx.x * D + d];
+    } else if (i < n_points) {
+        load_coords_strided<D>(cv, i, x);
+    }
+    return i < n_points;
+}
+
+// ---- per-level index / weight arithmetic ----------------------------------------------------
+
+template <int D>
+__device__ __forceinline__ void locate(const float (&x)[D], uint32_t res, uint32_t (&cell)[D], float (&t)[D]) {
+    const float r = static_cast<float>(res);
+#pragma unroll
+    for (int d = 0; d < D; ++d) {
+        const float pos = __fmul_rn(x[d], r);
+        const float fl = floorf(pos);
+        t[d] = __fsub_rn(pos, fl);
+        cell[d] = static_cast<uint32_t>(fl);  // saturating conversion: negative -> 0
+    }
+}
+
+template <int D>
+__device__ __forceinline__ void corner_weights(const float (&t)[D], float (&w)[1 << D]) {
+    float lo[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) lo[d] = __fsub_rn(1.f, t[d]);
+#pragma unroll
+    for (int c = 0; c < (1 << D); ++c) {
+        float p = (c & 1) ? t[0] : lo[0];
+#pragma unroll
+        for (int d = 1; d < D; ++d) p = __fmul_rn(p, ((c >> d) & 1) ? t[d] : lo[d]);
+        w[c] = p;
+    }
+}
+
+template <int D>
+__device__ __forceinline__ void corner_indices(const uint32_t (&cell)[D], const LevelParams &P, int level,
+                                               uint32_t (&idx)[1 << D]) {
+    const uint32_t res = P.res[level];
+    const uint32_t rows = P.rows[level];
+    const bool hashed = (P.hashed_mask >> level) & 1u;
+    if (!hashed) {
+        // term[d][b] = (cell_d + b) * res^d
+        uint32_t term[D][2];
+        uint32_t stride = 1;
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            term[d][0] = cell[d] * stride;
+            term[d][1] = term[d][0] + stride;
+            stride *= res;
+        }
+#pragma unroll
+        for (int c = 0; c < (1 << D); ++c) {
+            uint32_t h = term[0][c & 1];
+#pragma unroll
+            for (int d = 1; d < D; ++d) h += term[d][(c >> d) & 1];
+            // x == scale on every axis of a 1-D/2-D grid lands one row past the level; its weight is 0
+            idx[c] = min(h, rows - 1);
+        }
+    } else if ((P.pow2_mask >> level) & 1u) {
+        // low bits of the 64-bit products are all that survive "mod 2^k": wrap-around uint32 is exact
+        uint32_t term[D][2];
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            term[d][0] = cell[d] * P.primes[d];
+            term[d][1] = term[d][0] + P.primes[d];
+        }
+#pragma unroll
+        for (int c = 0; c < (1 << D); ++c) {
+            uint32_t h = term[0][c & 1];
+#pragma unroll
+            for (int d = 1; d < D; ++d) h ^= term[d][(c >> d) & 1];
+            idx[c] = h & (rows - 1);
+        }
+    } else {
+        unsigned long long term[D][2];
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            term[d][0] = static_cast<unsigned long long>(cell[d]) * P.primes[d];
+            term[d][1] = term[d][0] + P.primes[d];
+        }
+#pragma unroll
+        for (int c = 0; c < (1 << D); ++c) {
+            unsigned long long h = term[0][c & 1];
+#pragma unroll
+            for (int d = 1; d < D; ++d) h ^= term[d][(c >> d) & 1];
+            idx[c] = static_cast<uint32_t>(h % rows);
+        }
+    }
+}
+
+// ---- row access -----------------------------------------------------------------------------
+
+template <int BYTES>
+struct Packet;
+template <>
+struct Packet<2> { using type = unsigned short; };
+template <>
+struct Packet<4> { using type = unsigned int; };
+template <>
+struct Packet<8> { using type = uint2; };
+template <>
+struct Packet<16> { using type = uint4; };
+
+template <int BYTES>
+struct PacketBytes { static constexpr int value = BYTES >= 16 ? 16 : BYTES; };
+
+// COUNT consecutive elements of T <-> float registers, moved with the widest access that the
+// element count allows (2..16 bytes).  `p` must be aligned to that width.
+template <typename T, int COUNT, bool STREAM>
+__device__ __forceinline__ void load_elems(const T *p, float (&v)[COUNT]) {
+    constexpr int kBytes = COUNT * sizeof(T);
+    constexpr int kPk = PacketBytes<kBytes>::value;
+    using P = typename Packet<kPk>::type;
+    union { P pk[kBytes / kPk]; T el[COUNT]; } u;
+#pragma unroll
+    for (int k = 0; k < kBytes / kPk; ++k)
+        u.pk[k] = STREAM ? __ldcs(reinterpret_cast<const P *>(p) + k) : __ldg(reinterpret_cast<const P *>(p) + k);
+#pragma unroll
+    for (int k = 0; k < COUNT; ++k) v[k] = to_float<T>(u.el[k]);
+}
+
+template <typename T, int COUNT>
+__device__ __forceinline__ void store_elems(T *p, const float (&v)[COUNT], bool vector_ok) {
+    constexpr int kBytes = COUNT * sizeof(T);
+    constexpr int kPk = PacketBytes<kBytes>::value;
+    using P = typename Packet<kPk>::type;
+    union { P pk[kBytes / kPk]; T el[COUNT]; } u;
+#pragma unroll
+    for (int k = 0; k < COUNT; ++k) u.el[k] = from_float<T>(v[k]);
+    if (vector_ok) {
+#pragma unroll
+        for (int k = 0; k < kBytes / kPk; ++k) __stcs(reinterpret_cast<P *>(p) + k, u.pk[k]);
+    } else {
+#pragma unroll
+        for (int k = 0; k < COUNT; ++k) p[k] = u.el[k];
+    }
+}
+
+template <typename T, int COUNT>
+__device__ __forceinline__ void load_elems_checked(const T *p, float (&v)[COUNT], bool vector_ok) {
+    if (vector_ok) {
+        load_elems<T, COUNT, true>(p, v);
+    } else {
+#pragma unroll
+        for (int k = 0; k < COUNT; ++k) v[k] = to_float<T>(p[k]);
+    }
+}
+
+// One reduction per table row: red.global.add on F consecutive elements.
+template <int F>
+__device__ __forceinline__ void red_add_row(float *row, const float (&v)[F]) {
+    if constexpr (F == 1) {
+        asm volatile("red.global.add.f32 [%0], %1;" ::"l"(row), "f"(v[0]) : "memory");
+    } else if constexpr (F == 2) {
+        asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(row), "f"(v[0]), "f"(v[1]) : "memory");
+    } else {
+#pragma unroll
+        for (int k = 0; k < F; k += 4)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(row + k), "f"(v[k]), "f"(v[k + 1]),
+                         "f"(v[k + 2]), "f"(v[k + 3])
+                         : "memory");
+    }
+}
+
+__device__ __forceinline__ unsigned pack2(__half a, __half b) {
+    return static_cast<unsigned>(__half_as_ushort(a)) | (static_cast<unsigned>(__half_as_ushort(b)) << 16);
+}
+__device__ __forceinline__ unsigned pack2(__nv_bfloat16 a, __nv_bfloat16 b) {
+    return static_cast<unsigned>(__bfloat16_as_ushort(a)) | (static_cast<unsigned>(__bfloat16_as_ushort(b)) << 16);
+}
+
+template <int F>
+__device__ __forceinline__ void red_add_row(__half *row, const float (&v)[F]) {
+    if constexpr (F == 1) {
+        atomicAdd(row, __float2half_rn(v[0]));
+    } else if constexpr (F == 2) {
+        asm volatile("red.global.add.noftz.f16x2 [%0], %1;" ::"l"(row),
+                     "r"(pack2(__float2half_rn(v[0]), __float2half_rn(v[1])))
+                     : "memory");
+    } else {
+#pragma unroll
+        for (int k = 0; k < F; k += 4)
+            asm volatile("red.global.add.noftz.v2.f16x2 [%0], {%1, %2};" ::"l"(row + k),
+                         "r"(pack2(__float2half_rn(v[k]), __float2half_rn(v[k + 1]))),
+                         "r"(pack2(__float2half_rn(v[k + 2]), __float2half_rn(v[k + 3])))
+                         : "memory");
+    }
+}
+
+template <int F>
+__device__ __forceinline__ void red_add_row(__nv_bfloat16 *row, const float (&v)[F]) {
+    if constexpr (F == 1) {
+        atomicAdd(row, __float2bfloat16_rn(v[0]));
+    } else if constexpr (F == 2) {
+        asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(row),
+                     "r"(pack2(__float2bfloat16_rn(v[0]), __float2bfloat16_rn(v[1])))
+                     : "memory");
+    } else {
+#pragma unroll
+        for (int k = 0; k < F; k += 4)
+            asm volatile("red.global.add.noftz.v2.bf16x2 [%0], {%1, %2};" ::"l"(row + k),
+                         "r"(pack2(__float2bfloat16_rn(v[k]), __float2bfloat16_rn(v[k + 1]))),
+                         "r"(pack2(__float2bfloat16_rn(v[k + 2]), __float2bfloat16_rn(v[k + 3])))
+                         : "memory");
+    }
+}
+
+// ---- forward --------------------------------------------------------------------------------
+
+template <typename T, int D, int F, int LG>
+__global__ void __launch_bounds__(kThreads)
+hash_fwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, const T *__restrict__ table,
+                T *__restrict__ out, long long out_stride, long long n_points, int level_begin, int level_end,
+                int vector_ok) {
+    __shared__ __align__(16) float stage[kThreads * D];
+    float x[D];
+    const bool live = load_coords<D>(cv, n_points, x, stage);
+    if (!live) return;
+    if (P.scale != 1.f) {
+#pragma unroll
+        for (int d = 0; d < D; ++d) x[d] = __fdiv_rn(x[d], P.scale);
+    }
+    const long long i = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
+    T *out_row = out + i * out_stride;
+
+    for (int lg = level_begin; lg < level_end; lg += LG) {
+        float acc[LG * F];
+        float e[LG][1 << D][F];
+        float w[LG][1 << D];
+        // issue every gather of the group before the first use
+#pragma unroll
+        for (int j = 0; j < LG; ++j) {
+            const int level = lg + j;
+            uint32_t cell[D], idx[1 << D];
+            float t[D];
+            locate<D>(x, P.res[level], cell, t);
+            corner_weights<D>(t, w[j]);
+            corner_indices<D>(cell, P, level, idx);
+            const T *base = table + P.offset[level] * F;
+#pragma unroll
+            for (int c = 0; c < (1 << D); ++c)
+                load_elems<T, F, false>(base + static_cast<size_t>(idx[c]) * F, e[j][c]);
+        }
+#pragma unroll
+        for (int j = 0; j < LG; ++j) {
+#pragma unroll
+            for (int f = 0; f < F; ++f) {
+                float s = __fmul_rn(w[j][0], e[j][0][f]);
+#pragma unroll
+                for (int c = 1; c < (1 << D); ++c) s = __fadd_rn(s, __fmul_rn(w[j][c], e[j][c][f]));
+                acc[j * F + f] = s;
+            }
+        }
+        store_elems<T, LG * F>(out_row + lg * F, acc, vector_ok);
+    }
+}
+
+// ---- backward -------------------------------------------------------------------------------
+
+template <typename T, int D, int F, int LG>
+__global__ void __launch_bounds__(kThreads)
+hash_bwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, const T *__restrict__ grad_out,
+                long long go_stride, T *__restrict__ grad_table, long long n_points, int level_begin,
+                int level_end, int vector_ok) {
+    __shared__ __align__(16) float stage[kThreads * D];
+    float x[D];
+    const bool live = load_coords<D>(cv, n_points, x, stage);
+    // Dead lanes of the last CTA stay in the loop (the warp votes below need every lane)
+    // with zero gradient and are never chosen to issue an atomic.
+    if (P.scale != 1.f) {
+#pragma unroll
+        for (int d = 0; d < D; ++d) x[d] = __fdiv_rn(x[d], P.scale);
+    }
+    if (!live) {
+#pragma unroll
+        for (int d = 0; d < D; ++d) x[d] = 0.f;
+    }
+    const long long i = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
+    const T *go_row = grad_out + (live ? i : 0) * go_stride;
+    const unsigned lane = threadIdx.x & 31u;
+
+    for (int lg = level_begin; lg < level_end; lg += LG) {
+        float go[LG * F];
+        if (live) {
+            load_elems_checked<T, LG * F>(go_row + lg * F, go, vector_ok);
+        } else {
+#pragma unroll
+            for (int k = 0; k < LG * F; ++k) go[k] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < LG; ++j) {
+            const int level = lg + j;
+            uint32_t cell[D], idx[1 << D];
+            float t[D], w[1 << D];
+            locate<D>(x, P.res[level], cell, t);
+            corner_weights<D>(t, w);
+            corner_indices<D>(cell, P, level, idx);
+            T *base = grad_table + P.offset[level] * F;
+
+            // Lanes in the same cell share all 2^D rows.  The key packs the exact cell (21 bits per
+            // axis); dead lanes and cells too large to pack get a key nobody else has.
+            unsigned long long key = 0;
+            bool packable = live;
+#pragma unroll
+            for (int d = 0; d < D; ++d) {
+                packable = packable && cell[d] < (1u << 21);
+                key = (key << 21) | (cell[d] & 0x1fffffu);
+            }
+            if (!packable) key = (1ull << 63) | lane;
+            const unsigned peers = __match_any_sync(0xffffffffu, key);
+            const bool shared_cell = __any_sync(0xffffffffu, (peers & (peers - 1)) != 0);
+
+            if (!shared_cell) {
+                if (live) {
+#pragma unroll
+                    for (int c = 0; c < (1 << D); ++c) {
+                        float v[F];
+#pragma unroll
+                        for (int f = 0; f < F; ++f) v[f] = __fmul_rn(w[c], go[j * F + f]);
+                        red_add_row<F>(base + static_cast<size_t>(idx[c]) * F, v);
+                    }
+                }
+            } else {
+                const bool leader = (peers & ((1u << lane) - 1u)) == 0;
+                // longest peer list in the warp bounds the walk below
+                const int steps = __reduce_max_sync(0xffffffffu, __popc(peers));
+#pragma unroll
+                for (int c = 0; c < (1 << D); ++c) {
+                    float v[F], sum[F];
+#pragma unroll
+                    for (int f = 0; f < F; ++f) {
+                        v[f] = __fmul_rn(w[c], go[j * F + f]);
+                        sum[f] = 0.f;
+                    }
+                    // every lane walks its own peer list and ends up with its group's total
+                    unsigned rest = peers;
+                    for (int s = 0; s < steps; ++s) {
+                        const int src = rest ? (__ffs(rest) - 1) : static_cast<int>(lane);
+#pragma unroll
+                        for (int f = 0; f < F; ++f) {
+                            const float pv = __shfl_sync(0xffffffffu, v[f], src);
+                            if (rest) sum[f] += pv;
+                        }
+                        rest &= rest - 1;
+                    }
+                    if (live && leader) red_add_row<F>(base + static_cast<size_t>(idx[c]) * F, sum);
+                }
+            }
+        }
+    }
+}
+
+// ---- debug: indices and weights -------------------------------------------------------------
+
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+hash_debug_kernel(const __grid_constant__ LevelParams P, const CoordView cv, long long *__restrict__ idx_out,
+                  float *__restrict__ w_out, long long n_points, int n_levels) {
+    __shared__ __align__(16) float stage[kThreads * D];
+    float x[D];
+    if (!load_coords<D>(cv, n_points, x, stage)) return;
+    if (P.scale != 1.f) {
+#pragma unroll
+        for (int d = 0; d < D; ++d) x[d] = __fdiv_rn(x[d], P.scale);
+    }
+    const long long i = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
+    for (int level = 0; level < n_levels; ++level) {
+        uint32_t cell[D], idx[1 << D];
+        float t[D], w[1 << D];
+        locate<D>(x, P.res[level], cell, t);
+        corner_weights<D>(t, w);
+        corner_indices<D>(cell, P, level, idx);
+        const long long o = (i * n_levels + level) * (1 << D);
+#pragma unroll
+        for (int c = 0; c < (1 << D); ++c) {
+            idx_out[o + c] = idx[c];
+            if (w_out) w_out[o + c] = w[c];
+        }
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+
+int fill_params(LevelParams &P, int n_dims, int n_levels, const int32_t *res, const int64_t *rows,
+                const int64_t *offsets, const int64_t *primes, float scale) {
+    if (n_levels < 1 || n_levels > TH_MAX_LEVELS) return fail(TH_ERR_BAD_ARG, "n_levels %d outside [1, %d]", n_levels, TH_MAX_LEVELS);
+    if (n_dims < 1 || n_dims > TH_MAX_DIMS) return fail(TH_ERR_UNSUPPORTED, "n_dims %d outside [1, %d]", n_dims, TH_MAX_DIMS);
+    if (!res || !rows || !primes) return fail(TH_ERR_BAD_ARG, "null level array");
+    if (!(scale > 0.f)) return fail(TH_ERR_BAD_ARG, "scale must be positive");
+    P = LevelParams{};
+    P.scale = scale;
+    for (int d = 0; d < n_dims; ++d) {
+        if (primes[d] < 0 || primes[d] > 0xffffffffll) return fail(TH_ERR_BAD_ARG, "prime %d does not fit 32 bits", d);
+        P.primes[d] = static_cast<uint32_t>(primes[d]);
+    }
+    for (int l = 0; l < n_levels; ++l) {
+        if (res[l] < 1 || res[l] >= (1 << 24)) return fail(TH_ERR_BAD_ARG, "level %d resolution %d outside [1, 2^24)", l, res[l]);
+        if (rows[l] < 1 || rows[l] > 0xffffffffll) return fail(TH_ERR_BAD_ARG, "level %d row count out of range", l);
+        P.res[l] = static_cast<uint32_t>(res[l]);
+        P.rows[l] = static_cast<uint32_t>(rows[l]);
+        P.offset[l] = offsets ? static_cast<unsigned long long>(offsets[l]) : 0ull;
+        // dense iff (res + 1)^D <= rows  (kernel.py:453 of the reference)
+        unsigned long long dense_rows = 1;
+        for (int d = 0; d < n_dims; ++d) dense_rows *= static_cast<unsigned long long>(res[l]) + 1ull;
+        if (dense_rows > static_cast<unsigned long long>(rows[l])) P.hashed_mask |= 1u << l;
+        if ((rows[l] & (rows[l] - 1)) == 0) P.pow2_mask |= 1u << l;
+    }
+    return TH_OK;
+}
+
+int make_coord_view(CoordView &cv, const void *coords, int64_t stride_n, int64_t stride_d, int dtype, int n_dims) {
+    if (!coords) return fail(TH_ERR_BAD_ARG, "null coords");
+    if (dtype != TH_F32 && dtype != TH_F16 && dtype != TH_BF16) return fail(TH_ERR_BAD_ARG, "unknown coord dtype %d", dtype);
+    cv.ptr = coords;
+    cv.stride_n = stride_n;
+    cv.stride_d = stride_d;
+    cv.dtype = dtype;
+    cv.packed_f32 = dtype == TH_F32 && stride_d == 1 && stride_n == n_dims && aligned_to(coords, 16);
+    return TH_OK;
+}
+
+// Levels per register group: as many as divide the range, capped so a group holds <= 8 features.
+int pick_level_group(int level_begin, int level_end, int n_feats) {
+    const int count = level_end - level_begin;
+    const int cap = n_feats >= 8 ? 1 : (n_feats == 4 ? 2 : 4);
+    if (cap >= 4 && count % 4 == 0 && level_begin % 4 == 0) return 4;
+    if (cap >= 2 && count % 2 == 0 && level_begin % 2 == 0) return 2;
+    return 1;
+}
+
+template <typename T, int D, int F>
+int launch_fwd(const LevelParams &P, const CoordView &cv, const void *table, void *out, int64_t out_stride,
+               int64_t n, int l0, int l1, cudaStream_t stream) {
+    const unsigned grid = static_cast<unsigned>((n + kThreads - 1) / kThreads);
+    const int vec = aligned_to(out, 16) && (out_stride * sizeof(T)) % 16 == 0;
+    const T *tb = static_cast<const T *>(table);
+    T *o = static_cast<T *>(out);
+    switch (pick_level_group(l0, l1, F)) {
+        case 4: hash_fwd_kernel<T, D, F, 4><<<grid, kThreads, 0, stream>>>(P, cv, tb, o, out_stride, n, l0, l1, vec); break;
+        case 2: hash_fwd_kernel<T, D, F, 2><<<grid, kThreads, 0, stream>>>(P, cv, tb, o, out_stride, n, l0, l1, vec); break;
+        default: hash_fwd_kernel<T, D, F, 1><<<grid, kThreads, 0, stream>>>(P, cv, tb, o, out_stride, n, l0, l1, vec); break;
+    }
+    return cuda_status(cudaGetLastError(), "hash_fwd_kernel launch");
+}
+
+template <typename T, int D, int F>
+int launch_bwd(const LevelParams &P, const CoordView &cv, const void *go, int64_t go_stride, void *grad_table,
+               int64_t n, int l0, int l1, cudaStream_t stream) {
+    const unsigned grid = static_cast<unsigned>((n + kThreads - 1) / kThreads);
+    const int vec = aligned_to(go, 16) && (go_stride * sizeof(T)) % 16 == 0;
+    const T *g = static_cast<const T *>(go);
+    T *gt = static_cast<T *>(grad_table);
+    switch (pick_level_group(l0, l1, F)) {
+        case 4: hash_bwd_kernel<T, D, F, 4><<<grid, kThreads, 0, stream>>>(P, cv, g, go_stride, gt, n, l0, l1, vec); break;
+        case 2: hash_bwd_kernel<T, D, F, 2><<<grid, kThreads, 0, stream>>>(P, cv, g, go_stride, gt, n, l0, l1, vec); break;
+        default: hash_bwd_kernel<T, D, F, 1><<<grid, kThreads, 0, stream>>>(P, cv, g, go_stride, gt, n, l0, l1, vec); break;
+    }
+    return cuda_status(cudaGetLastError(), "hash_bwd_kernel launch");
+}
+
+// Expands (dtype, D, F) into a template instantiation.
+#define TH_DISPATCH_F(T, D, CALL)                                                      \
+    switch (n_feats) {                                                                 \
+        case 1: return CALL(T, D, 1);                                                  \
+        case 2: return CALL(T, D, 2);                                                  \
+        case 4: return CALL(T, D, 4);                                                  \
+        case 8: return CALL(T, D, 8);                                                  \
+        default: return fail(TH_ERR_UNSUPPORTED, "n_feats %d not in {1, 2, 4, 8}", n_feats); \
+    }
+#define TH_DISPATCH_D(T, CALL)                    \
+    switch (n_dims) {                             \
+        case 1: TH_DISPATCH_F(T, 1, CALL)         \
+        case 2: TH_DISPATCH_F(T, 2, CALL)         \
+        default: TH_DISPATCH_F(T, 3, CALL)        \
+    }
+#define TH_DISPATCH(CALL)                                                                  \
+    switch (table_dtype) {                                                                 \
+        case TH_F32: TH_DISPATCH_D(float, CALL)                                            \
+        case TH_F16: TH_DISPATCH_D(__half, CALL)                                           \
+        case TH_BF16: TH_DISPATCH_D(__nv_bfloat16, CALL)                                   \
+        default: return fail(TH_ERR_BAD_ARG, "unknown table dtype %d", table_dtype);       \
+    }
+
+int check_range(int n_levels, int l0, int l1) {
+    if (l0 < 0 || l1 > n_levels || l0 >= l1) return fail(TH_ERR_BAD_ARG, "level range [%d, %d) outside [0, %d)", l0, l1, n_levels);
+    return TH_OK;
+}
+
+}  // namespace
+}  // namespace th
+
+using namespace th;
+
+extern "C" int th_hash_fwd(const void *coords_dev, int64_t coord_stride_n, int64_t coord_stride_d, int coord_dtype,
+                           const void *table_dev, int table_dtype, void *out_dev, int64_t out_stride_n,
+                           int64_t n_points, int n_dims, int n_feats, int n_levels, const int32_t *level_res_host,
+                           const int64_t *level_rows_host, const int64_t *level_offset_host,
+                           const int64_t *primes_host, float scale, int level_begin, int level_end, void *stream) {
+    if (n_points < 0) return fail(TH_ERR_BAD_ARG, "negative n_points");
+    LevelParams P;
+    CoordView cv;
+    if (int rc = fill_params(P, n_dims, n_levels, level_res_host, level_rows_host, level_offset_host, primes_host, scale)) return rc;
+    if (!level_offset_host) return fail(TH_ERR_BAD_ARG, "null level offsets");
+    if (int rc = check_range(n_levels, level_begin, level_end)) return rc;
+    if (n_points == 0) return TH_OK;
+    if (int rc = make_coord_view(cv, coords_dev, coord_stride_n, coord_stride_d, coord_dtype, n_dims)) return rc;
+    if (!table_dev || !out_dev) return fail(TH_ERR_BAD_ARG, "null table or output");
+    const size_t row_bytes = n_feats * dtype_bytes(table_dtype);
+    if (!aligned_to(table_dev, row_bytes < 16 ? row_bytes : 16)) return fail(TH_ERR_ALIGNMENT, "table rows must be aligned to min(row bytes, 16)");
+    if (out_stride_n < static_cast<int64_t>(n_levels) * n_feats) return fail(TH_ERR_BAD_ARG, "out_stride_n smaller than n_levels * n_feats");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define TH_CALL_FWD(T, D, F) launch_fwd<T, D, F>(P, cv, table_dev, out_dev, out_stride_n, n_points, level_begin, level_end, s)
+    TH_DISPATCH(TH_CALL_FWD)
+#undef TH_CALL_FWD
+}
+
+extern "C" int th_hash_bwd(const void *coords_dev, int64_t coord_stride_n, int64_t coord_stride_d, int coord_dtype,
+                           const void *grad_out_dev, int64_t go_stride_n, void *grad_table_dev, int table_dtype,
+                           int64_t n_points, int n_dims, int n_feats, int n_levels, const int32_t *level_res_host,
+                           const int64_t *level_rows_host, const int64_t *level_offset_host,
+                           const int64_t *primes_host, float scale, int level_begin, int level_end, void *stream) {
+    if (n_points < 0) return fail(TH_ERR_BAD_ARG, "negative n_points");
+    LevelParams P;
+    CoordView cv;
+    if (int rc = fill_params(P, n_dims, n_levels, level_res_host, level_rows_host, level_offset_host, primes_host, scale)) return rc;
+    if (!level_offset_host) return fail(TH_ERR_BAD_ARG, "null level offsets");
+    if (int rc = check_range(n_levels, level_begin, level_end)) return rc;
+    if (n_points == 0) return TH_OK;
+    if (int rc = make_coord_view(cv, coords_dev, coord_stride_n, coord_stride_d, coord_dtype, n_dims)) return rc;
+    if (!grad_out_dev || !grad_table_dev) return fail(TH_ERR_BAD_ARG, "null gradient pointer");
+    const size_t row_bytes = n_feats * dtype_bytes(table_dtype);
+    if (!aligned_to(grad_table_dev, row_bytes < 16 ? row_bytes : 16)) return fail(TH_ERR_ALIGNMENT, "table rows must be aligned to min(row bytes, 16)");
+    if (go_stride_n < static_cast<int64_t>(n_levels) * n_feats) return fail(TH_ERR_BAD_ARG, "go_stride_n smaller than n_levels * n_feats");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define TH_CALL_BWD(T, D, F) launch_bwd<T, D, F>(P, cv, grad_out_dev, go_stride_n, grad_table_dev, n_points, level_begin, level_end, s)
+    TH_DISPATCH(TH_CALL_BWD)
+#undef TH_CALL_BWD
+}
+
+extern "C" int th_hash_debug_indices(const void *coords_dev, int64_t coord_stride_n, int64_t coord_stride_d,
+                                     int coord_dtype, int64_t *idx_out_dev, float *weight_out_dev, int64_t n_points,
+                                     int n_dims, int n_levels, const int32_t *level_res_host,
+                                     const int64_t *level_rows_host, const int64_t *primes_host, float scale,
+                                     void *stream) {
+    if (n_points < 0) return fail(TH_ERR_BAD_ARG, "negative n_points");
+    LevelParams P;
+    CoordView cv;
+    if (int rc = fill_params(P, n_dims, n_levels, level_res_host, level_rows_host, nullptr, primes_host, scale)) return rc;
+    if (n_points == 0) return TH_OK;
+    if (int rc = make_coord_view(cv, coords_dev, coord_stride_n, coord_stride_d, coord_dtype, n_dims)) return rc;
+    if (!idx_out_dev) return fail(TH_ERR_BAD_ARG, "null index output");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const unsigned grid = static_cast<unsigned>((n_points + kThreads - 1) / kThreads);
+    long long *io = reinterpret_cast<long long *>(idx_out_dev);
+    switch (n_dims) {
+        case 1: hash_debug_kernel<1><<<grid, kThreads, 0, s>>>(P, cv, io, weight_out_dev, n_points, n_levels); break;
+        case 2: hash_debug_kernel<2><<<grid, kThreads, 0, s>>>(P, cv, io, weight_out_dev, n_points, n_levels); break;
+        default: hash_debug_kernel<3><<<grid, kThreads, 0, s>>>(P, cv, io, weight_out_dev, n_points, n_levels); break;
+    }
+    return cuda_status(cudaGetLastError(), "hash_debug_kernel launch");
+}
