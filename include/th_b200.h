@@ -115,6 +115,77 @@ int th_hash_debug_indices(const void *coords_dev, int64_t coord_stride_n, int64_
                           const int32_t *level_res_host, const int64_t *level_rows_host,
                           const int64_t *primes_host, float scale, void *stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Fully fused MLP:  y = W_out . act(W_hid[depth-2] . ... act(W_in . x + b_in) ...) + b_out
+ *
+ * Weights are row-major (out, in) like nn.Linear: w_in (d_hidden, d_in), w_hid
+ * ((depth-1) * d_hidden, d_hidden), w_out (d_out, d_hidden); biases b_in (d_hidden), b_hid
+ * (depth-1, d_hidden), b_out (d_out), either all given or all null.  depth counts the activated
+ * layers (input layer + depth-1 hidden layers), as in
+ * triton_helpers/layers/fully_fused_mlp/kernel.py:534-542.  Every dimension is <= 64 and
+ * d_hidden is a power of two >= 16 (kernel.py:525-531).  dtype is TH_F16 or TH_BF16 for x, all
+ * parameters, outputs and gradients; accumulation is fp32 (fp16_acc is accepted and ignored).
+ * x / out / grad rows are `*_stride` elements apart with unit stride inside a row.
+ * ------------------------------------------------------------------------------------------ */
+
+/* Forward: replaces the launch in _fully_fused_mlp.forward
+ * (triton_helpers/layers/fully_fused_mlp/kernel.py:553-562 -> _fwd_kernel :198-261). */
+int th_mlp_fwd(const void *x_dev, int64_t x_stride, const void *w_in_dev, const void *b_in_dev,
+               const void *w_hid_dev, const void *b_hid_dev, const void *w_out_dev, const void *b_out_dev,
+               void *out_dev, int64_t out_stride, int64_t rows, int d_in, int d_hidden, int d_out, int depth,
+               int activation, int dtype, int fp16_acc, void *stream);
+
+/* Bytes of fp32 scratch th_mlp_bwd needs (one float per parameter); -1 for an unsupported shape. */
+int64_t th_mlp_workspace_bytes(int d_in, int d_hidden, int d_out, int depth);
+
+/* Backward: replaces the launch and the torch .sum(0) reductions of _fully_fused_mlp.backward
+ * (triton_helpers/layers/fully_fused_mlp/kernel.py:599-633 -> _bwd_kernel_rfs :326-500).
+ * Writes grad_x (rows, d_in) and the parameter gradients in `dtype`; any gradient pointer may be
+ * null to skip it.  workspace_dev is caller-provided scratch of th_mlp_workspace_bytes() bytes;
+ * the call zero-fills it, accumulates fp32 partial sums there and rounds once at the end. */
+int th_mlp_bwd(const void *x_dev, int64_t x_stride, const void *w_in_dev, const void *b_in_dev,
+               const void *w_hid_dev, const void *b_hid_dev, const void *w_out_dev, const void *b_out_dev,
+               const void *grad_out_dev, int64_t go_stride, void *grad_x_dev, int64_t gx_stride,
+               void *grad_w_in_dev, void *grad_b_in_dev, void *grad_w_hid_dev, void *grad_b_hid_dev,
+               void *grad_w_out_dev, void *grad_b_out_dev, void *workspace_dev, int64_t workspace_bytes,
+               int64_t rows, int d_in, int d_hidden, int d_out, int depth, int activation, int dtype,
+               int fp16_acc, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Reversible (additive coupling) fused MLP.  NO COUNTERPART IN THE REFERENCE: triton_helpers
+ * has no reversible operator; the conventions (stacked (out, in) weights, 16-bit operands,
+ * fp32 accumulation) are those of its fused MLP (fully_fused_mlp/kernel.py:503-686).
+ *
+ *   x = [x1 | x2] (rows, d_model), halves of width H = d_model / 2.  Block k:
+ *     y1 = x1 + F_k(x2),   F_k(u) = W_f2[k] . act(W_f1[k] . u + b_f1[k]) + b_f2[k]
+ *     y2 = x2 + G_k(y1),   G_k(u) = W_g2[k] . act(W_g1[k] . u + b_g1[k]) + b_g2[k]
+ *   w_f1, w_g1: (blocks * d_hidden, H);  w_f2, w_g2: (blocks * H, d_hidden), row-major, 16-byte
+ *   aligned; biases (blocks, d_hidden) / (blocks, H), all given or all null.  d_model is a
+ *   multiple of 32 up to 128, d_hidden a multiple of 16 up to 64; dtype TH_F16 or TH_BF16.
+ * ------------------------------------------------------------------------------------------ */
+
+int th_rev_fwd(const void *x_dev, int64_t x_stride, const void *w_f1_dev, const void *w_f2_dev,
+               const void *w_g1_dev, const void *w_g2_dev, const void *b_f1_dev, const void *b_f2_dev,
+               const void *b_g1_dev, const void *b_g2_dev, void *out_dev, int64_t out_stride, int64_t rows,
+               int d_model, int d_hidden, int blocks, int activation, int dtype, void *stream);
+
+/* Bytes of fp32 scratch th_rev_bwd needs for `rows` rows: one private copy of all weight-gradient
+ * accumulators per resident CTA (about 0.5 MB per CTA for 8 blocks of 64 x 64). */
+int64_t th_rev_workspace_bytes(int64_t rows, int d_model, int d_hidden, int blocks);
+
+/* Backward from the stack's OUTPUT y (no stored activations): reconstructs the inputs block by
+ * block (x2 = y2 - G(y1), x1 = y1 - F(x2)) while forming the gradients.  Writes grad_x, the
+ * eight parameter gradients (any may be null) and, when x_rec_dev is not null, the reconstructed
+ * input, for checking the reconstruction error. */
+int th_rev_bwd(const void *y_dev, int64_t y_stride, const void *w_f1_dev, const void *w_f2_dev,
+               const void *w_g1_dev, const void *w_g2_dev, const void *b_f1_dev, const void *b_f2_dev,
+               const void *b_g1_dev, const void *b_g2_dev, const void *grad_out_dev, int64_t go_stride,
+               void *grad_x_dev, int64_t gx_stride, void *x_rec_dev, int64_t xr_stride, void *grad_w_f1_dev,
+               void *grad_w_f2_dev, void *grad_w_g1_dev, void *grad_w_g2_dev, void *grad_b_f1_dev,
+               void *grad_b_f2_dev, void *grad_b_g1_dev, void *grad_b_g2_dev, void *workspace_dev,
+               int64_t workspace_bytes, int64_t rows, int d_model, int d_hidden, int blocks, int activation,
+               int dtype, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

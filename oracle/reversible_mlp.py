@@ -112,3 +112,75 @@ def forward_backward(
     y.backward(grad_out.to(torch.float32))
     grads = tuple(None if p is None else p.grad for p in leaves[1:])
     return y.detach(), leaves[0].grad, grads
+
+
+@torch.no_grad()
+def forward_backward_storage_rounded(
+    x: Tensor,
+    weights: Sequence[Tensor],
+    biases: Sequence[Optional[Tensor]],
+    grad_out: Tensor,
+    activation: str = "relu",
+):
+    r"""The stack with the fused kernels' rounding points and the reconstructing backward.
+
+    Arithmetic being restated (float32 everywhere except where noted): the residual stream stays
+    float32 inside a pass; each branch input, hidden activation and pre-activation is rounded to
+    the storage dtype before it is used as a matrix operand; the output of the forward pass is
+    rounded to the storage dtype (it is what gets saved); the backward pass starts from that
+    rounded output, reconstructs ``x2 = y2 - G(y1)`` and ``x1 = y1 - F(x2)`` block by block,
+    and rounds the branch-output gradient and ``dz`` to the storage dtype before they are used as
+    matrix operands.  Returns ``(y, dx, grads(8), x_reconstructed)`` in float32.
+    """
+    from .fused_mlp import activation_grad
+
+    dtype = x.dtype
+    rnd = lambda t: t.to(dtype).to(torch.float32)  # noqa: E731
+    params = _to_f32((*weights, *biases))
+    half = x.shape[-1] // 2
+    hidden = weights[1].shape[-1]
+    blocks = weights[0].shape[0] // hidden
+    lead = x.shape[:-1]
+    xf = x.to(torch.float32).reshape(-1, 2 * half)
+
+    def branch(u, w1, b1, w2, b2):
+        z = F.linear(rnd(u), w1, b1)
+        h = rnd(activation_fn(activation, z))
+        return F.linear(h, w2, b2), rnd(z), h
+
+    s1, s2 = xf[:, :half].clone(), xf[:, half:].clone()
+    for k in range(blocks):
+        f, g = _split(params, k, half, hidden)
+        s1 = s1 + branch(s2, *f)[0]
+        s2 = s2 + branch(s1, *g)[0]
+    y = rnd(torch.cat([s1, s2], -1))
+
+    s1, s2 = y[:, :half].clone(), y[:, half:].clone()
+    go = rnd(grad_out.to(torch.float32).reshape(-1, 2 * half))
+    d1, d2 = go[:, :half].clone(), go[:, half:].clone()
+    has_bias = biases[0] is not None
+    dw = [torch.zeros_like(p) for p in params[:4]]
+    db = [torch.zeros_like(p) if has_bias else None for p in (params[4:] if has_bias else [None] * 4)]
+    for k in reversed(range(blocks)):
+        f, g = _split(params, k, half, hidden)
+        for (w1, b1, w2, b2), m1, in_is_first in ((g, 2, True), (f, 0, False)):
+            in_s, out_d = (s1, d2) if in_is_first else (s2, d1)
+            out, z, h = branch(in_s, w1, b1, w2, b2)
+            if in_is_first:
+                s2 = s2 - out
+            else:
+                s1 = s1 - out
+            dy = rnd(out_d)
+            dz = rnd(activation_grad(activation, z, dy @ w2))
+            dw[m1 + 1][k * half : (k + 1) * half] = dy.t() @ h
+            dw[m1][k * hidden : (k + 1) * hidden] = dz.t() @ rnd(in_s)
+            if has_bias:
+                db[m1 + 1][k] = dy.sum(0)
+                db[m1][k] = dz.sum(0)
+            if in_is_first:
+                d1 = d1 + dz @ w1
+            else:
+                d2 = d2 + dz @ w1
+    dx = rnd(torch.cat([d1, d2], -1)).reshape(*lead, -1)
+    x_rec = rnd(torch.cat([s1, s2], -1)).reshape(*lead, -1)
+    return y.reshape(*lead, -1), dx, (*dw, *db), x_rec

@@ -41,6 +41,28 @@ SIGNATURES = {
         [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, _I32P, _I64P, _I64P,
          c_float, c_void_p],
     ),
+    "th_mlp_fwd": (
+        c_int,
+        [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    ),
+    "th_mlp_workspace_bytes": (c_int64, [c_int, c_int, c_int, c_int]),
+    "th_mlp_bwd": (
+        c_int,
+        [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+         c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+         c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    ),
+    "th_rev_fwd": (
+        c_int,
+        [c_void_p, c_int64] + [c_void_p] * 8 + [c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    ),
+    "th_rev_workspace_bytes": (c_int64, [c_int64, c_int, c_int, c_int]),
+    "th_rev_bwd": (
+        c_int,
+        [c_void_p, c_int64] + [c_void_p] * 8 + [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64]
+        + [c_void_p] * 8 + [c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    ),
 }  # fmt: skip
 
 

@@ -1,0 +1,180 @@
+r"""Fully fused small MLP on hand-written sm_100a kernels.
+
+Drop-in for ``triton_helpers/layers/fully_fused_mlp/kernel.py``: ``_fully_fused_mlp`` is the
+``torch.autograd.Function`` (reference :503-637) and ``fully_fused_mlp`` the functional wrapper
+(reference :640-686) with the same argument order, assertions and 9-tuple of gradients.  The
+Triton launches are replaced by ``th_mlp_fwd`` / ``th_mlp_bwd`` of ``libth_b200.so``.
+
+Differences a caller can observe:
+
+* float16 and bfloat16 only.  The reference also takes float32 tensors (``tl.dot`` in TF32);
+  here a float32 call raises ``TypeError`` (under autocast everything is cast to float16 first,
+  as in the reference, so module use is unaffected).
+* ``fp16_acc`` is accepted and ignored: accumulation is always float32.
+* biases may be ``None`` (all of them) for a bias-free network; the reference requires tensors.
+* the Triton device functions the reference re-exports (``feedforward`` ...) do not exist.
+"""
+from typing import Final, Optional
+
+import torch
+from torch import Tensor
+from torch.autograd import Function
+
+from ... import _lib
+from ...ops import ensure_str
+
+# Above this size the weights no longer stay on chip (reference :13-14)
+FULLY_FUSED_MAX_DIM: Final = 64
+ACTIVATIONS: Final = ("relu", "relu2", "silu", "none")
+
+
+def _rows_view(t: Tensor) -> Tensor:
+    r"""``(B, L, D)`` tensor whose ``B * L`` rows are evenly strided with unit stride inside a row."""
+    B, L, _ = t.shape
+    if t.stride(2) != 1 or (B > 1 and t.stride(0) != L * t.stride(1)) or t.stride(1) < t.shape[2]:
+        t = t.contiguous()
+    return t
+
+
+def _check_dtype(*tensors: Optional[Tensor]) -> torch.dtype:
+    dtypes = {t.dtype for t in tensors if t is not None}
+    if len(dtypes) != 1:
+        raise TypeError(f"input and parameters must share one dtype, got {dtypes}")
+    (dtype,) = dtypes
+    if dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError(f"fused MLP kernels take float16 or bfloat16 tensors, got {dtype}")
+    return dtype
+
+
+class _fully_fused_mlp(Function):
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.float16)
+    @torch.no_grad()
+    def forward(
+        ctx,
+        x: Tensor,
+        w_in: Tensor,
+        b_in: Optional[Tensor],
+        w_out: Tensor,
+        b_out: Optional[Tensor],
+        w_hid: Optional[Tensor],
+        b_hid: Optional[Tensor],
+        activation: str = "relu",
+        fp16_acc: bool = False,
+    ) -> Tensor:
+        B, L, D = x.shape
+        D_hidden, D_in = w_in.shape
+        D_out, _ = w_out.shape
+        assert D_in == D, "Input dimension mismatch"
+        assert D_hidden == w_out.shape[-1], "Hidden dimension mismatch"
+
+        assert D_in <= FULLY_FUSED_MAX_DIM, f"Input dimension {D_in} too large for full fusion"
+        assert D_hidden <= FULLY_FUSED_MAX_DIM, f"Hidden dimension {D_hidden} too large for full fusion"
+        assert D_out <= FULLY_FUSED_MAX_DIM, f"Output dimension {D_out} too large for full fusion"
+        assert D_hidden & (D_hidden - 1) == 0, "Hidden dimension must be a power of 2"
+        assert D_hidden >= 16, "Hidden dimension must be at least 16"
+
+        if w_hid is not None and w_hid.numel() > 0:
+            depth = w_hid.shape[0] // D_hidden
+            assert w_hid.shape == (depth * D_hidden, D_hidden), "Hidden weight shape mismatch"
+            assert b_hid is None or b_hid.shape == (depth, D_hidden), "Hidden bias shape mismatch"
+            depth += 1
+        else:
+            depth = 1
+            w_hid = b_hid = None
+        assert activation in ACTIVATIONS, f"Invalid activation function: {activation}"
+        has_bias = b_in is not None
+        assert (b_out is not None) == has_bias and (depth == 1 or (b_hid is not None) == has_bias), (
+            "Biases must be given for every layer or for none"
+        )
+
+        device = _lib.require_cuda(x, w_in, b_in, w_out, b_out, w_hid, b_hid)
+        dtype = _check_dtype(x, w_in, b_in, w_out, b_out, w_hid, b_hid)
+        x = _rows_view(x)
+        w_in, w_out = w_in.contiguous(), w_out.contiguous()
+        w_hid = None if w_hid is None else w_hid.contiguous()
+        b_in, b_out, b_hid = (None if b is None else b.contiguous() for b in (b_in, b_out, b_hid))
+
+        o = x.new_empty((B, L, D_out))
+        with torch.cuda.device(device):
+            _lib.check(
+                _lib.lib().th_mlp_fwd(
+                    x.data_ptr(), x.stride(1), w_in.data_ptr(), _lib.ptr(b_in), _lib.ptr(w_hid), _lib.ptr(b_hid),
+                    w_out.data_ptr(), _lib.ptr(b_out), o.data_ptr(), D_out, B * L, D_in, D_hidden, D_out, depth,
+                    _lib.ACTIVATION_CODE[activation], _lib.DTYPE_CODE[dtype], int(fp16_acc), _lib.stream_ptr(device),
+                ),
+                "th_mlp_fwd",
+            )  # fmt: skip
+
+        ctx.save_for_backward(x, w_in, b_in, w_out, b_out, w_hid, b_hid)
+        ctx.activation = activation
+        ctx.fp16_acc = fp16_acc
+        ctx.depth = depth
+        return o
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    @torch.no_grad()
+    def backward(ctx, do: Tensor):
+        x, w_in, b_in, w_out, b_out, w_hid, b_hid = ctx.saved_tensors
+        B, L, D_in = x.shape
+        D_hidden, _ = w_in.shape
+        D_out, _ = w_out.shape
+        depth = ctx.depth
+        device, dtype = x.device, x.dtype
+
+        if do.dtype != dtype:
+            do = do.to(dtype)
+        do = _rows_view(do)
+
+        dx = x.new_empty((B, L, D_in))
+        dw_in, dw_out = torch.empty_like(w_in), torch.empty_like(w_out)
+        dw_hid = None if w_hid is None else torch.empty_like(w_hid)
+        db_in, db_out, db_hid = (None if b is None else torch.empty_like(b) for b in (b_in, b_out, b_hid))
+        ws_bytes = _lib.lib().th_mlp_workspace_bytes(D_in, D_hidden, D_out, depth)
+        workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=device)
+        with torch.cuda.device(device):
+            _lib.check(
+                _lib.lib().th_mlp_bwd(
+                    x.data_ptr(), x.stride(1), w_in.data_ptr(), _lib.ptr(b_in), _lib.ptr(w_hid), _lib.ptr(b_hid),
+                    w_out.data_ptr(), _lib.ptr(b_out), do.data_ptr(), do.stride(1), dx.data_ptr(), D_in,
+                    dw_in.data_ptr(), _lib.ptr(db_in), _lib.ptr(dw_hid), _lib.ptr(db_hid), dw_out.data_ptr(),
+                    _lib.ptr(db_out), workspace.data_ptr(), ws_bytes, B * L, D_in, D_hidden, D_out, depth,
+                    _lib.ACTIVATION_CODE[ctx.activation], _lib.DTYPE_CODE[dtype], int(ctx.fp16_acc),
+                    _lib.stream_ptr(device),
+                ),
+                "th_mlp_bwd",
+            )  # fmt: skip
+        return dx, dw_in, db_in, dw_out, db_out, dw_hid, db_hid, None, None
+
+
+def fully_fused_mlp(
+    x: Tensor,
+    w_in: Tensor,
+    b_in: Optional[Tensor],
+    w_out: Tensor,
+    b_out: Optional[Tensor],
+    w_hid: Optional[Tensor] = None,
+    b_hid: Optional[Tensor] = None,
+    activation: str = "relu",
+    fp16_acc: bool = False,
+) -> Tensor:
+    r"""Forward pass of a multi-layer perceptron in a single kernel (Mueller et al., arXiv:2106.12372).
+
+    Args:
+        x: Input tensor
+        w_in, b_in: Weight and bias of the input layer
+        w_out, b_out: Weight and bias of the (never activated) output layer
+        w_hid, b_hid: Stacked weights and biases of the hidden layers, or ``None`` for a single layer
+        activation: ``"relu"``, ``"relu2"``, ``"silu"`` or ``"none"``
+        fp16_acc: accepted for compatibility; accumulation is always float32
+
+    Shapes:
+        - x: :math:`(B, L, D_{in})`, output :math:`(B, L, D_{out})`
+        - w_in: :math:`(D_{hidden}, D_{in})`, b_in: :math:`(D_{hidden},)`
+        - w_out: :math:`(D_{out}, D_{hidden})`, b_out: :math:`(D_{out},)`
+        - w_hid: :math:`(depth \cdot D_{hidden}, D_{hidden})`, b_hid: :math:`(depth, D_{hidden})`
+    """
+    activation = ensure_str(activation)
+    return _fully_fused_mlp.apply(x, w_in, b_in, w_out, b_out, w_hid, b_hid, activation, fp16_acc)
