@@ -186,6 +186,27 @@ int th_rev_bwd(const void *y_dev, int64_t y_stride, const void *w_f1_dev, const 
                int64_t workspace_bytes, int64_t rows, int d_model, int d_hidden, int blocks, int activation,
                int dtype, void *stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Element-wise steps of a training step around the fused operators.  NO COUNTERPART IN THE
+ * REFERENCE (triton_helpers stops at forward/backward); they keep the data-parallel
+ * neural-field step on hand-written kernels from the loss to the parameter update.
+ * All tensors 32-byte aligned and contiguous.
+ * ------------------------------------------------------------------------------------------ */
+
+/* grad[i] = (pred[i] - target[i]) * grad_scale in `dtype`; adds sum (pred - target)^2 to
+ * *loss_sum_dev (fp32, caller-zeroed; may be null). */
+int th_mse_grad(const void *pred_dev, const void *target_dev, void *grad_dev, float *loss_sum_dev,
+                int64_t n_elems, float grad_scale, int dtype, void *stream);
+
+/* One Adam step (torch.optim.Adam semantics, no weight decay, no amsgrad) on `dtype` parameters
+ * with fp32 moments: g = grad * grad_scale; m, v updated; param -= lr / (1 - beta1^step) * m /
+ * (sqrt(v) / sqrt(1 - beta2^step) + eps).  step counts from 1.  With zero_grad != 0 the gradient
+ * buffer is cleared in the same pass (the table gradient must start at zero every step,
+ * triton_helpers/layers/hash_encoding/kernel.py:636). */
+int th_adam_step(void *param_dev, void *grad_dev, float *exp_avg_dev, float *exp_avg_sq_dev, int64_t n_elems,
+                 float lr, float beta1, float beta2, float eps, int step, float grad_scale, int zero_grad,
+                 int dtype, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

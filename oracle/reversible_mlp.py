@@ -121,8 +121,12 @@ def forward_backward_storage_rounded(
     biases: Sequence[Optional[Tensor]],
     grad_out: Tensor,
     activation: str = "relu",
+    y_saved: Optional[Tensor] = None,
 ):
     r"""The stack with the fused kernels' rounding points and the reconstructing backward.
+
+    ``y_saved`` (optional) replaces the forward result as the tensor the backward pass starts
+    from: pass the output another implementation produced to check its backward in isolation.
 
     Arithmetic being restated (float32 everywhere except where noted): the residual stream stays
     float32 inside a pass; each branch input, hidden activation and pre-activation is rounded to
@@ -155,6 +159,8 @@ def forward_backward_storage_rounded(
         s2 = s2 + branch(s1, *g)[0]
     y = rnd(torch.cat([s1, s2], -1))
 
+    if y_saved is not None:
+        y = y_saved.to(torch.float32).reshape(-1, 2 * half)
     s1, s2 = y[:, :half].clone(), y[:, half:].clone()
     go = rnd(grad_out.to(torch.float32).reshape(-1, 2 * half))
     d1, d2 = go[:, :half].clone(), go[:, half:].clone()

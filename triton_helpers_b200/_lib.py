@@ -63,11 +63,78 @@ SIGNATURES = {
         [c_void_p, c_int64] + [c_void_p] * 8 + [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64]
         + [c_void_p] * 8 + [c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p],
     ),
+    "th_mse_grad": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_int, c_void_p]),
+    "th_adam_step": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_float, c_float, c_float, c_int, c_float, c_int,
+         c_int, c_void_p],
+    ),
 }  # fmt: skip
 
 
+class KernelTimer:
+    r"""Collects CUDA-event timings of every launching C-ABI call made while it is active.
+
+    Events are recorded on the stream the call launches on (torch's current stream), directly
+    before and after the call, so the difference is the device time of the kernels that call
+    queued.  ``summary()`` synchronises and returns ``{entry point: (calls, total ms)}``.
+    """
+
+    LAUNCHING = ("th_hash_fwd", "th_hash_bwd", "th_mlp_fwd", "th_mlp_bwd", "th_rev_fwd", "th_rev_bwd",
+                 "th_mse_grad", "th_adam_step")  # fmt: skip
+
+    def __init__(self):
+        self.records = []
+
+    def __enter__(self):
+        global _ACTIVE_TIMER
+        _ACTIVE_TIMER = self
+        return self
+
+    def __exit__(self, *exc):
+        global _ACTIVE_TIMER
+        _ACTIVE_TIMER = None
+        return False
+
+    def summary(self):
+        torch.cuda.synchronize()
+        out = {}
+        for name, start, stop in self.records:
+            calls, total = out.get(name, (0, 0.0))
+            out[name] = (calls + 1, total + start.elapsed_time(stop))
+        return out
+
+
+_ACTIVE_TIMER: Optional[KernelTimer] = None
+
+
+class _Library:
+    r"""Thin proxy over the ``ctypes.CDLL``: same attribute names, optional event timing."""
+
+    def __init__(self, handle: ctypes.CDLL):
+        self._handle = handle
+        for name in SIGNATURES:
+            raw = getattr(handle, name)
+            setattr(self, name, self._timed(name, raw) if name in KernelTimer.LAUNCHING else raw)
+
+    @staticmethod
+    def _timed(name, raw):
+        def call(*args):
+            timer = _ACTIVE_TIMER
+            if timer is None:
+                return raw(*args)
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            code = raw(*args)
+            stop.record()
+            timer.records.append((name, start, stop))
+            return code
+
+        return call
+
+
 @lru_cache(maxsize=1)
-def lib() -> ctypes.CDLL:
+def lib() -> _Library:
     if not LIB_PATH.exists():
         raise RuntimeError(
             f"{LIB_PATH} is missing: build the CUDA extension with `python -m triton_helpers_b200.build` "
@@ -78,7 +145,7 @@ def lib() -> ctypes.CDLL:
         fn = getattr(handle, name)
         fn.restype = restype
         fn.argtypes = argtypes
-    return handle
+    return _Library(handle)
 
 
 def check(code: int, what: str) -> None:

@@ -21,20 +21,22 @@ class FullyFusedMLP(nn.Module):
         depth: int,
         activation: str = "relu",
         fp16_acc: bool = False,
+        bias: bool = True,
     ):
+        # ``bias=False`` (an extension; the reference always has biases) builds a bias-free network
         super().__init__()
-        first = nn.Linear(d_in, d_hidden)
+        first = nn.Linear(d_in, d_hidden, bias=bias)
         self.w_in = first.weight
         self.b_in = first.bias
 
         if depth > 1:
-            hidden = [nn.Linear(d_hidden, d_hidden) for _ in range(depth - 1)]
+            hidden = [nn.Linear(d_hidden, d_hidden, bias=bias) for _ in range(depth - 1)]
             self.w_hid = nn.Parameter(torch.cat([layer.weight for layer in hidden], 0))
-            self.b_hid = nn.Parameter(torch.stack([layer.bias for layer in hidden], 0))
+            self.b_hid = nn.Parameter(torch.stack([layer.bias for layer in hidden], 0)) if bias else None
         else:
             self.w_hid = self.b_hid = None
 
-        last = nn.Linear(d_hidden, d_out)
+        last = nn.Linear(d_hidden, d_out, bias=bias)
         self.w_out = last.weight
         self.b_out = last.bias
 

@@ -1,0 +1,96 @@
+r"""Neural-field training step: hash encoding -> fused MLP -> MSE -> backward -> gradient sum -> Adam.
+
+The step BASELINE configuration 3 describes, built only from this package's operators.  It
+has no counterpart in triton_helpers (which stops at the two layers); the layers it drives are
+the drop-in ``HashEncoding`` and ``FullyFusedMLP`` modules, so everything between the coordinates
+and the parameter update runs in the hand-written kernels: ``th_hash_fwd``, ``th_mlp_fwd``,
+``th_mse_grad``, ``th_mlp_bwd``, ``th_hash_bwd``, ``th_adam_step``.  With more than one process
+the point batch is split across ranks, parameters are replicated and their gradients summed once
+per step (``parallel.allreduce_gradients``).
+"""
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+from torch import Tensor
+
+from . import _lib
+from .layers.fully_fused_mlp import FullyFusedMLP
+from .layers.hash_encoding import HashEncoding
+from .optim import FusedAdam
+from .parallel import allreduce_gradients
+
+
+@torch.no_grad()
+def mse_grad(pred: Tensor, target: Tensor, grad_scale: float) -> Tuple[Tensor, Tensor]:
+    r"""``(grad, loss_sum)``: ``grad = (pred - target) * grad_scale`` in ``pred``'s dtype and the
+    float32 sum of squared differences (a one-element device tensor), in one kernel."""
+    assert pred.shape == target.shape and pred.dtype == target.dtype, "Prediction / target mismatch"
+    device = _lib.require_cuda(pred, target)
+    pred, target = pred.contiguous(), target.contiguous()
+    grad = torch.empty_like(pred)
+    loss_sum = torch.zeros(1, dtype=torch.float32, device=device)
+    with torch.cuda.device(device):
+        _lib.check(
+            _lib.lib().th_mse_grad(
+                pred.data_ptr(), target.data_ptr(), grad.data_ptr(), loss_sum.data_ptr(), pred.numel(), grad_scale,
+                _lib.dtype_code(pred), _lib.stream_ptr(device),
+            ),
+            "th_mse_grad",
+        )  # fmt: skip
+    return grad, loss_sum
+
+
+class NeuralFieldTrainer(nn.Module):
+    r"""Hash-encoded MLP regressed on targets with MSE and Adam.
+
+    Args:
+        encoding, mlp: the two layers (moved to the device and dtype the caller wants; float16
+            tables and weights for BASELINE configuration 3).
+        lr, betas, eps: Adam hyper-parameters.
+        grad_out_scale: the MLP receives ``(pred - target) * grad_out_scale`` as its output
+            gradient, i.e. the loss is scaled so 16-bit gradients neither underflow nor overflow;
+            Adam undoes the scale exactly.
+        group: process group for data parallelism (``None``: the default group, if initialised).
+    """
+
+    def __init__(
+        self,
+        encoding: HashEncoding,
+        mlp: FullyFusedMLP,
+        lr: float = 1e-2,
+        betas: Tuple[float, float] = (0.9, 0.99),
+        eps: float = 1e-15,
+        grad_out_scale: float = 1.0 / 16.0,
+        group: Optional[dist.ProcessGroup] = None,
+    ):
+        super().__init__()
+        self.encoding = encoding
+        self.mlp = mlp
+        self.grad_out_scale = grad_out_scale
+        self.group = group
+        self.optimizer = FusedAdam(self.parameters(), lr=lr, betas=betas, eps=eps)
+
+    def world_size(self) -> int:
+        return dist.get_world_size(self.group) if dist.is_available() and dist.is_initialized() else 1
+
+    def forward(self, coords: Tensor) -> Tensor:
+        r"""Prediction ``(N, d_out)`` for coordinates ``(N, D)``."""
+        return self.mlp(self.encoding(coords).unsqueeze(0)).squeeze(0)
+
+    def step(self, coords: Tensor, targets: Tensor) -> Tensor:
+        r"""One optimisation step on this rank's points; returns the local mean squared error
+        (float32, on the device, not synchronised)."""
+        pred = self.forward(coords)
+        grad_out, loss_sum = mse_grad(pred, targets.to(pred.dtype), self.grad_out_scale)
+        pred.backward(grad_out)
+        world = self.world_size()
+        grads = [p.grad for p in self.parameters() if p.grad is not None]
+        allreduce_gradients(grads, self.group)
+        # d(mean over the global batch)/d pred = 2 (pred - target) / (N_global * C)
+        true_over_stored = 2.0 / (pred.numel() * world * self.grad_out_scale)
+        self.optimizer.step(grad_scale=true_over_stored)
+        for p in self.parameters():
+            p.grad = None
+        return loss_sum / pred.numel()
