@@ -151,6 +151,30 @@ int th_mlp_bwd(const void *x_dev, int64_t x_stride, const void *w_in_dev, const 
                int64_t rows, int d_in, int d_hidden, int d_out, int depth, int activation, int dtype,
                int fp16_acc, void *stream);
 
+/* Backward of the fused MLP for callers that cannot hand over scratch memory.  It has no
+ * counterpart in the reference.  Arguments and results are those of th_mlp_bwd without the
+ * workspace pair: the fp32 scratch is a 256 KB array that is part of the library image, so every
+ * GPU that loads the library carries it until the process ends, and nothing is allocated or freed
+ * by the call.  Meant for hosts where device memory cannot be requested at call time (the
+ * application gave the whole device to its own pool, a latency-critical loop must avoid the
+ * device-wide synchronisation an allocation implies, or a C caller has no allocator at hand).
+ *   - Networks whose parameters exceed th_mlp_bwd_static_max_bytes() / 4 floats are refused with
+ *     TH_ERR_WORKSPACE; use th_mlp_bwd with caller scratch for those.
+ *   - The first call on a device looks up the array's device address (that device must be
+ *     current); make that first call before any stream capture begins.
+ *   - All calls on a device share the one array, which still holds the previous call's sums when
+ *     the next begins: each call clears the part it uses on its stream before accumulating, and
+ *     two calls whose GPU work overlaps (different streams or threads) race on it. */
+int th_mlp_bwd_static(const void *x_dev, int64_t x_stride, const void *w_in_dev, const void *b_in_dev,
+                      const void *w_hid_dev, const void *b_hid_dev, const void *w_out_dev, const void *b_out_dev,
+                      const void *grad_out_dev, int64_t go_stride, void *grad_x_dev, int64_t gx_stride,
+                      void *grad_w_in_dev, void *grad_b_in_dev, void *grad_w_hid_dev, void *grad_b_hid_dev,
+                      void *grad_w_out_dev, void *grad_b_out_dev, int64_t rows, int d_in, int d_hidden, int d_out,
+                      int depth, int activation, int dtype, int fp16_acc, void *stream);
+
+/* Size in bytes of the built-in scratch th_mlp_bwd_static uses (262144). */
+int64_t th_mlp_bwd_static_max_bytes(void);
+
 /* ------------------------------------------------------------------------------------------
  * Reversible (additive coupling) fused MLP.  NO COUNTERPART IN THE REFERENCE: triton_helpers
  * has no reversible operator; the conventions (stacked (out, in) weights, 16-bit operands,

@@ -53,6 +53,13 @@ SIGNATURES = {
          c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
          c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     ),
+    "th_mlp_bwd_static": (
+        c_int,
+        [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+         c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    ),
+    "th_mlp_bwd_static_max_bytes": (c_int64, []),
     "th_rev_fwd": (
         c_int,
         [c_void_p, c_int64] + [c_void_p] * 8 + [c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p],

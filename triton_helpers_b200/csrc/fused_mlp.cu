@@ -24,6 +24,8 @@
 // rounds the workspace into the gradient tensors.
 #include "mma_tiles.cuh"
 
+#include <mutex>
+
 namespace th {
 namespace {
 
@@ -514,4 +516,64 @@ extern "C" int th_mlp_bwd(const void *x_dev, int64_t x_stride, const void *w_in_
                                                  grad_w_out_dev, grad_b_out_dev, ws, rows, st);
         default: return fail(TH_ERR_UNSUPPORTED, "fused MLP kernels take float16 or bfloat16 (dtype code %d)", dtype);
     }
+}
+
+// ---- backward without caller-provided scratch ------------------------------------------------
+//
+// th_mlp_bwd needs one fp32 per parameter of scratch and asks the caller for it.  Some callers
+// have no way to get device memory at call time: a plug-in inside a host application that
+// handed the whole device to its own memory pool, a latency-critical loop that must not run
+// into the device-wide synchronisation cudaMalloc implies, or a plain C caller with no
+// allocator at hand.  For them the scratch below is part of the library image: every GPU
+// that loads the library holds these 256 KB until the process exits.
+
+namespace {
+
+constexpr int kStaticScratchFloats = 64 * 1024;  // 256 KB: e.g. fourteen 64 x 64 layers
+
+static __device__ __align__(256) float g_mlp_bwd_scratch[kStaticScratchFloats];
+
+// In host code `g_mlp_bwd_scratch` is only a handle for the runtime, not a device address, so the
+// address the kernels get is looked up once per device (with that device current) and cached.
+int static_scratch_address(float **out) {
+    static std::mutex guard;
+    static float *cache[64] = {nullptr};
+    int dev = -1;
+    if (int rc = th::cuda_status(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+    if (dev < 0 || dev >= 64) return th::fail(TH_ERR_UNSUPPORTED, "device ordinal %d outside [0, 64)", dev);
+    std::lock_guard<std::mutex> lock(guard);
+    if (!cache[dev]) {
+        void *address = nullptr;
+        if (int rc = th::cuda_status(cudaGetSymbolAddress(&address, g_mlp_bwd_scratch), "cudaGetSymbolAddress(scratch)"))
+            return rc;
+        cache[dev] = static_cast<float *>(address);
+    }
+    *out = cache[dev];
+    return TH_OK;
+}
+
+}  // namespace
+
+extern "C" int64_t th_mlp_bwd_static_max_bytes(void) { return static_cast<int64_t>(sizeof(float)) * kStaticScratchFloats; }
+
+extern "C" int th_mlp_bwd_static(const void *x_dev, int64_t x_stride, const void *w_in_dev, const void *b_in_dev,
+                                 const void *w_hid_dev, const void *b_hid_dev, const void *w_out_dev,
+                                 const void *b_out_dev, const void *grad_out_dev, int64_t go_stride, void *grad_x_dev,
+                                 int64_t gx_stride, void *grad_w_in_dev, void *grad_b_in_dev, void *grad_w_hid_dev,
+                                 void *grad_b_hid_dev, void *grad_w_out_dev, void *grad_b_out_dev, int64_t rows,
+                                 int d_in, int d_hidden, int d_out, int depth, int activation, int dtype, int fp16_acc,
+                                 void *stream) {
+    const int64_t need = th_mlp_workspace_bytes(d_in, d_hidden, d_out, depth);
+    if (need < 0) return fail(TH_ERR_UNSUPPORTED, "unsupported layer shape %d -> %d x %d -> %d", d_in, depth, d_hidden, d_out);
+    if (need > th_mlp_bwd_static_max_bytes())
+        return fail(TH_ERR_WORKSPACE,
+                    "this network needs %lld bytes of scratch, the built-in buffer holds %lld: use th_mlp_bwd with caller scratch",
+                    (long long)need, (long long)th_mlp_bwd_static_max_bytes());
+    float *scratch = nullptr;
+    if (int rc = static_scratch_address(&scratch)) return rc;
+    // same launch sequence as th_mlp_bwd; it zero-fills the part of the scratch it uses first
+    return th_mlp_bwd(x_dev, x_stride, w_in_dev, b_in_dev, w_hid_dev, b_hid_dev, w_out_dev, b_out_dev, grad_out_dev,
+                      go_stride, grad_x_dev, gx_stride, grad_w_in_dev, grad_b_in_dev, grad_w_hid_dev, grad_b_hid_dev,
+                      grad_w_out_dev, grad_b_out_dev, scratch, need, rows, d_in, d_hidden, d_out, depth, activation,
+                      dtype, fp16_acc, stream);
 }
