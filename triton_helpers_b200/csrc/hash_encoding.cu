@@ -8,17 +8,23 @@
 //   hashed : index = xor_d(corner_d * prime_d) mod rows
 //   t      = x * res - cell ;  weight(corner) = prod_d (bit_d ? t_d : 1 - t_d), axis order 0,1,2
 //
-// Work decomposition: one thread per point, 256 points per CTA.  The CTA stages its
-// coordinates through shared memory with 128-bit coalesced loads; each thread then walks
-// the levels in register groups of LG levels, so the LG * 2^D row gathers of a group are
-// all in flight together, and writes (forward) or reads (backward) its slice of the
-// [N, L*F] matrix with 128-bit accesses.  Tables are read through the read-only path and
-// are meant to stay L2 resident; outputs and incoming gradients are streamed.
+// Work decomposition: TWO neighbouring lanes per point, 128 points per CTA.  Lane 0 of a pair
+// takes the 2^(D-1) corners on the low-x side of the cell, lane 1 those on the high-x side.
+// Rows of x-neighbours are adjacent in a dense level and, because the first hashing prime is
+// 1, differ only in their low bits in a hashed level, so the two addresses a lane pair
+// presents in one load / reduction instruction fall into the same 32-byte sector most of the
+// time (7 in 8 for 4-byte rows) and the memory system handles them as one transaction; with
+// one thread per point they would be two transactions from two instructions.  The CTA stages
+// its coordinates through shared memory with 128-bit coalesced loads; each lane then walks the
+// levels in register groups of LG levels, so the gathers of a whole group are in flight
+// together; a pair combines its two partial sums with one shuffle and each lane writes
+// (forward) half of the group's slice of the [N, L*F] matrix.  Tables are read through the
+// read-only path and are meant to stay L2 resident; outputs and gradients are streamed.
 //
-// Backward contention: lanes of a warp that fall in the same cell of a level are found
-// with one match.any per level; their contributions are summed in registers and the first
-// lane of each group issues a single vector red.global.add per corner, so a cluster of
-// points costs one memory atomic per corner instead of one per point.
+// Backward contention: lanes of a warp that work on the same cell and side are found with one
+// match.any per level; their contributions are summed in registers and the first lane of
+// each group issues a single vector red.global.add per corner, so a cluster of points costs
+// one memory atomic per corner instead of one per point.
 #include "common.cuh"
 
 namespace th {
@@ -60,15 +66,18 @@ __device__ __forceinline__ void load_coords_strided(const CoordView &cv, long lo
     }
 }
 
-// The CTA's 256 * D floats are contiguous: fetch them as float4, then each thread picks its D values.
-template <int D>
+// LPP lanes work on one point, so a CTA covers kThreads / LPP points.  Their D floats each are
+// contiguous: fetch them as float4, then every lane picks the D values of its point.
+template <int D, int LPP>
 __device__ __forceinline__ bool load_coords(const CoordView &cv, long long n_points, float (&x)[D], float *stage) {
-    const long long i = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
+    constexpr int kPoints = kThreads / LPP;
+    const int local = threadIdx.x / LPP;
+    const long long i = static_cast<long long>(blockIdx.x) * kPoints + local;
     if (cv.packed_f32) {
-        const long long first = static_cast<long long>(blockIdx.x) * kThreads * D;  // multiple of 4
+        const long long first = static_cast<long long>(blockIdx.x) * kPoints * D;  // multiple of 4
         const long long total = n_points * D;
         const float *src = static_cast<const float *>(cv.ptr);
-        for (int v = threadIdx.x; v < kThreads * D / 4; v += kThreads) {
+        for (int v = threadIdx.x; v < kPoints * D / 4; v += kThreads) {
             const long long e = first + 4ll * v;
             if (e + 3 < total) {
                 reinterpret_cast<float4 *>(stage)[v] = __ldcs(reinterpret_cast<const float4 *>(src + e));
@@ -79,7 +88,7 @@ __device__ __forceinline__ bool load_coords(const CoordView &cv, long long n_poi
         }
         __syncthreads();
 #pragma unroll
-        for (int d = 0; d < D; ++d) x[d] = stage[threadIdx.x * D + d];
+        for (int d = 0; d < D; ++d) x[d] = stage[local * D + d];
     } else if (i < n_points) {
         load_coords_strided<D>(cv, i, x);
     }
@@ -166,6 +175,76 @@ __device__ __forceinline__ void corner_indices(const uint32_t (&cell)[D], const 
 #pragma unroll
             for (int d = 1; d < D; ++d) h ^= term[d][(c >> d) & 1];
             idx[c] = static_cast<uint32_t>(h % rows);
+        }
+    }
+}
+
+// The 2^(D-1) corners on one x-side of the cell (side 0: low x, side 1: high x), in the order of
+// the remaining axes' bits; same arithmetic as corner_weights / corner_indices above.
+template <int D>
+__device__ __forceinline__ void side_weights(const float (&t)[D], int side, float (&w)[1 << (D - 1)]) {
+    const float wx = side ? t[0] : __fsub_rn(1.f, t[0]);
+    float lo[D];
+#pragma unroll
+    for (int d = 1; d < D; ++d) lo[d] = __fsub_rn(1.f, t[d]);
+#pragma unroll
+    for (int j = 0; j < (1 << (D - 1)); ++j) {
+        float p = wx;
+#pragma unroll
+        for (int d = 1; d < D; ++d) p = __fmul_rn(p, ((j >> (d - 1)) & 1) ? t[d] : lo[d]);
+        w[j] = p;
+    }
+}
+
+template <int D>
+__device__ __forceinline__ void side_indices(const uint32_t (&cell)[D], const LevelParams &P, int level, int side,
+                                             uint32_t (&idx)[1 << (D - 1)]) {
+    const uint32_t res = P.res[level];
+    const uint32_t rows = P.rows[level];
+    const bool hashed = (P.hashed_mask >> level) & 1u;
+    if (!hashed) {
+        uint32_t term[D][2];
+        uint32_t stride = 1;
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            term[d][0] = cell[d] * stride;
+            term[d][1] = term[d][0] + stride;
+            stride *= res;
+        }
+#pragma unroll
+        for (int j = 0; j < (1 << (D - 1)); ++j) {
+            uint32_t h = side ? term[0][1] : term[0][0];
+#pragma unroll
+            for (int d = 1; d < D; ++d) h += term[d][(j >> (d - 1)) & 1];
+            idx[j] = min(h, rows - 1);
+        }
+    } else if ((P.pow2_mask >> level) & 1u) {
+        uint32_t term[D][2];
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            term[d][0] = cell[d] * P.primes[d];
+            term[d][1] = term[d][0] + P.primes[d];
+        }
+#pragma unroll
+        for (int j = 0; j < (1 << (D - 1)); ++j) {
+            uint32_t h = side ? term[0][1] : term[0][0];
+#pragma unroll
+            for (int d = 1; d < D; ++d) h ^= term[d][(j >> (d - 1)) & 1];
+            idx[j] = h & (rows - 1);
+        }
+    } else {
+        unsigned long long term[D][2];
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            term[d][0] = static_cast<unsigned long long>(cell[d]) * P.primes[d];
+            term[d][1] = term[d][0] + P.primes[d];
+        }
+#pragma unroll
+        for (int j = 0; j < (1 << (D - 1)); ++j) {
+            unsigned long long h = side ? term[0][1] : term[0][0];
+#pragma unroll
+            for (int d = 1; d < D; ++d) h ^= term[d][(j >> (d - 1)) & 1];
+            idx[j] = static_cast<uint32_t>(h % rows);
         }
     }
 }
@@ -294,34 +373,42 @@ __global__ void __launch_bounds__(kThreads)
 hash_fwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, const T *__restrict__ table,
                 T *__restrict__ out, long long out_stride, long long n_points, int level_begin, int level_end,
                 int vector_ok) {
-    __shared__ __align__(16) float stage[kThreads * D];
+    constexpr int kPoints = kThreads / 2;
+    constexpr int kSide = 1 << (D - 1);   // corners per lane
+    constexpr int kCount = LG * F;        // outputs per level group
+    constexpr int kFirst = (kCount + 1) / 2;  // written by lane 0 of the pair; the rest by lane 1
+    __shared__ __align__(16) float stage[kPoints * D];
     float x[D];
-    const bool live = load_coords<D>(cv, n_points, x, stage);
-    if (!live) return;
+    const bool live = load_coords<D, 2>(cv, n_points, x, stage);
+    // dead pairs of the last CTA stay in the loop: the pair shuffle below needs both lanes
     if (P.scale != 1.f) {
 #pragma unroll
         for (int d = 0; d < D; ++d) x[d] = __fdiv_rn(x[d], P.scale);
     }
-    const long long i = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
-    T *out_row = out + i * out_stride;
+    if (!live) {
+#pragma unroll
+        for (int d = 0; d < D; ++d) x[d] = 0.f;
+    }
+    const int side = threadIdx.x & 1;
+    const long long i = static_cast<long long>(blockIdx.x) * kPoints + (threadIdx.x >> 1);
+    T *out_row = out + (live ? i : 0) * out_stride;
 
     for (int lg = level_begin; lg < level_end; lg += LG) {
-        float acc[LG * F];
-        float e[LG][1 << D][F];
-        float w[LG][1 << D];
+        float acc[kCount];
+        float e[LG][kSide][F];
+        float w[LG][kSide];
         // issue every gather of the group before the first use
 #pragma unroll
         for (int j = 0; j < LG; ++j) {
             const int level = lg + j;
-            uint32_t cell[D], idx[1 << D];
+            uint32_t cell[D], idx[kSide];
             float t[D];
             locate<D>(x, P.res[level], cell, t);
-            corner_weights<D>(t, w[j]);
-            corner_indices<D>(cell, P, level, idx);
+            side_weights<D>(t, side, w[j]);
+            side_indices<D>(cell, P, level, side, idx);
             const T *base = table + P.offset[level] * F;
 #pragma unroll
-            for (int c = 0; c < (1 << D); ++c)
-                load_elems<T, F, false>(base + static_cast<size_t>(idx[c]) * F, e[j][c]);
+            for (int c = 0; c < kSide; ++c) load_elems<T, F, false>(base + static_cast<size_t>(idx[c]) * F, e[j][c]);
         }
 #pragma unroll
         for (int j = 0; j < LG; ++j) {
@@ -329,11 +416,24 @@ hash_fwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, const
             for (int f = 0; f < F; ++f) {
                 float s = __fmul_rn(w[j][0], e[j][0][f]);
 #pragma unroll
-                for (int c = 1; c < (1 << D); ++c) s = __fadd_rn(s, __fmul_rn(w[j][c], e[j][c][f]));
-                acc[j * F + f] = s;
+                for (int c = 1; c < kSide; ++c) s = __fadd_rn(s, __fmul_rn(w[j][c], e[j][c][f]));
+                // low-x side + high-x side
+                acc[j * F + f] = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 1));
             }
         }
-        store_elems<T, LG * F>(out_row + lg * F, acc, vector_ok);
+        if (live) {
+            if (side == 0) {
+                float part[kFirst];
+#pragma unroll
+                for (int k = 0; k < kFirst; ++k) part[k] = acc[k];
+                store_elems<T, kFirst>(out_row + lg * F, part, vector_ok);
+            } else if constexpr (kCount - kFirst > 0) {
+                float part[kCount - kFirst];
+#pragma unroll
+                for (int k = 0; k < kCount - kFirst; ++k) part[k] = acc[kFirst + k];
+                store_elems<T, kCount - kFirst>(out_row + lg * F + kFirst, part, vector_ok);
+            }
+        }
     }
 }
 
@@ -344,9 +444,11 @@ __global__ void __launch_bounds__(kThreads)
 hash_bwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, const T *__restrict__ grad_out,
                 long long go_stride, T *__restrict__ grad_table, long long n_points, int level_begin,
                 int level_end, int vector_ok) {
-    __shared__ __align__(16) float stage[kThreads * D];
+    constexpr int kPoints = kThreads / 2;
+    constexpr int kSide = 1 << (D - 1);
+    __shared__ __align__(16) float stage[kPoints * D];
     float x[D];
-    const bool live = load_coords<D>(cv, n_points, x, stage);
+    const bool live = load_coords<D, 2>(cv, n_points, x, stage);
     // Dead lanes of the last CTA stay in the loop (the warp votes below need every lane)
     // with zero gradient and are never chosen to issue an atomic.
     if (P.scale != 1.f) {
@@ -357,14 +459,15 @@ hash_bwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, const
 #pragma unroll
         for (int d = 0; d < D; ++d) x[d] = 0.f;
     }
-    const long long i = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
+    const int side = threadIdx.x & 1;
+    const long long i = static_cast<long long>(blockIdx.x) * kPoints + (threadIdx.x >> 1);
     const T *go_row = grad_out + (live ? i : 0) * go_stride;
     const unsigned lane = threadIdx.x & 31u;
 
     for (int lg = level_begin; lg < level_end; lg += LG) {
         float go[LG * F];
         if (live) {
-            load_elems_checked<T, LG * F>(go_row + lg * F, go, vector_ok);
+            load_elems_checked<T, LG * F>(go_row + lg * F, go, vector_ok);  // both lanes of a pair: one broadcast load
         } else {
 #pragma unroll
             for (int k = 0; k < LG * F; ++k) go[k] = 0.f;
@@ -372,22 +475,24 @@ hash_bwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, const
 #pragma unroll
         for (int j = 0; j < LG; ++j) {
             const int level = lg + j;
-            uint32_t cell[D], idx[1 << D];
-            float t[D], w[1 << D];
+            uint32_t cell[D], idx[kSide];
+            float t[D], w[kSide];
             locate<D>(x, P.res[level], cell, t);
-            corner_weights<D>(t, w);
-            corner_indices<D>(cell, P, level, idx);
+            side_weights<D>(t, side, w);
+            side_indices<D>(cell, P, level, side, idx);
             T *base = grad_table + P.offset[level] * F;
 
-            // Lanes in the same cell share all 2^D rows.  The key packs the exact cell (21 bits per
-            // axis); dead lanes and cells too large to pack get a key nobody else has.
+            // Lanes on the same side of the same cell share all their rows.  The key packs the exact
+            // cell (20 bits per axis) and the side; dead lanes and cells too large to pack get a key
+            // nobody else has.
             unsigned long long key = 0;
             bool packable = live;
 #pragma unroll
             for (int d = 0; d < D; ++d) {
-                packable = packable && cell[d] < (1u << 21);
-                key = (key << 21) | (cell[d] & 0x1fffffu);
+                packable = packable && cell[d] < (1u << 20);
+                key = (key << 20) | (cell[d] & 0xfffffu);
             }
+            key = (key << 1) | static_cast<unsigned>(side);
             if (!packable) key = (1ull << 63) | lane;
             const unsigned peers = __match_any_sync(0xffffffffu, key);
             const bool shared_cell = __any_sync(0xffffffffu, (peers & (peers - 1)) != 0);
@@ -395,7 +500,7 @@ hash_bwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, const
             if (!shared_cell) {
                 if (live) {
 #pragma unroll
-                    for (int c = 0; c < (1 << D); ++c) {
+                    for (int c = 0; c < kSide; ++c) {
                         float v[F];
 #pragma unroll
                         for (int f = 0; f < F; ++f) v[f] = __fmul_rn(w[c], go[j * F + f]);
@@ -407,7 +512,7 @@ hash_bwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, const
                 // longest peer list in the warp bounds the walk below
                 const int steps = __reduce_max_sync(0xffffffffu, __popc(peers));
 #pragma unroll
-                for (int c = 0; c < (1 << D); ++c) {
+                for (int c = 0; c < kSide; ++c) {
                     float v[F], sum[F];
 #pragma unroll
                     for (int f = 0; f < F; ++f) {
@@ -440,7 +545,7 @@ hash_debug_kernel(const __grid_constant__ LevelParams P, const CoordView cv, lon
                   float *__restrict__ w_out, long long n_points, int n_levels) {
     __shared__ __align__(16) float stage[kThreads * D];
     float x[D];
-    if (!load_coords<D>(cv, n_points, x, stage)) return;
+    if (!load_coords<D, 1>(cv, n_points, x, stage)) return;
     if (P.scale != 1.f) {
 #pragma unroll
         for (int d = 0; d < D; ++d) x[d] = __fdiv_rn(x[d], P.scale);
@@ -513,7 +618,7 @@ int pick_level_group(int level_begin, int level_end, int n_feats) {
 template <typename T, int D, int F>
 int launch_fwd(const LevelParams &P, const CoordView &cv, const void *table, void *out, int64_t out_stride,
                int64_t n, int l0, int l1, cudaStream_t stream) {
-    const unsigned grid = static_cast<unsigned>((n + kThreads - 1) / kThreads);
+    const unsigned grid = static_cast<unsigned>((n + kThreads / 2 - 1) / (kThreads / 2));
     const int vec = aligned_to(out, 16) && (out_stride * sizeof(T)) % 16 == 0;
     const T *tb = static_cast<const T *>(table);
     T *o = static_cast<T *>(out);
@@ -528,7 +633,7 @@ int launch_fwd(const LevelParams &P, const CoordView &cv, const void *table, voi
 template <typename T, int D, int F>
 int launch_bwd(const LevelParams &P, const CoordView &cv, const void *go, int64_t go_stride, void *grad_table,
                int64_t n, int l0, int l1, cudaStream_t stream) {
-    const unsigned grid = static_cast<unsigned>((n + kThreads - 1) / kThreads);
+    const unsigned grid = static_cast<unsigned>((n + kThreads / 2 - 1) / (kThreads / 2));
     const int vec = aligned_to(go, 16) && (go_stride * sizeof(T)) % 16 == 0;
     const T *g = static_cast<const T *>(go);
     T *gt = static_cast<T *>(grad_table);
