@@ -135,6 +135,11 @@ int th_mlp_fwd(const void *x_dev, int64_t x_stride, const void *w_in_dev, const 
                void *out_dev, int64_t out_stride, int64_t rows, int d_in, int d_hidden, int d_out, int depth,
                int activation, int dtype, int fp16_acc, void *stream);
 
+/* Device-side status word of the tensor-core MLP kernels: 0 = fine, 1 = one of their bounded waits
+ * ran out (the kernel then returned early and its results are invalid).  Synchronises the device.
+ * No counterpart in the reference. */
+int th_mlp_tc_status(void);
+
 /* Bytes of fp32 scratch th_mlp_bwd needs (one float per parameter); -1 for an unsupported shape. */
 int64_t th_mlp_workspace_bytes(int d_in, int d_hidden, int d_out, int depth);
 

@@ -22,9 +22,11 @@
 // 128 rows, accumulated in fp32 shared-memory slots that live for the whole kernel and are
 // flushed once per CTA with red.global.add into an fp32 workspace.  A small second kernel
 // rounds the workspace into the gradient tensors.
+#include "mlp_shape.cuh"
 #include "mma_tiles.cuh"
 
 #include <mutex>
+#include <type_traits>
 
 namespace th {
 namespace {
@@ -35,19 +37,6 @@ constexpr int kFwdMT = 2;                       // 16-row tiles per warp in the 
 constexpr int kFwdRows = kWarps * 16 * kFwdMT;  // rows per CTA iteration (forward)
 constexpr int kBwdRows = kWarps * 16;           // rows per CTA iteration (backward)
 constexpr int kSmemLimit = 227 * 1024;
-
-struct MlpShape {
-    int d_in, d_hid, d_out;
-    int depth;    // activated layers: the input layer plus depth-1 hidden layers
-    int ki, h, no;  // d_in, d_hid, d_out padded to multiples of 16
-    int act;
-    int has_bias;
-};
-
-struct MlpParams {
-    const void *w_in, *w_hid, *w_out;
-    const void *b_in, *b_hid, *b_out;
-};
 
 // Shared-memory layout, computed identically on host and device.
 struct MlpSmem {
@@ -162,31 +151,6 @@ mlp_fwd_kernel(const MlpShape s, const MlpParams p, const T *__restrict__ x, lon
 }
 
 // ---- backward -------------------------------------------------------------------------------
-
-struct MlpGradWorkspace {
-    float *base;  // fp32, laid out as [w_in | w_hid | w_out | b_in | b_hid | b_out], unpadded
-    int w_in, w_hid, w_out, b_in, b_hid, b_out, total;
-};
-
-__host__ __device__ inline MlpGradWorkspace grad_workspace_layout(const MlpShape &s, float *base) {
-    MlpGradWorkspace w{};
-    w.base = base;
-    int off = 0;
-    w.w_in = off;
-    off += s.d_hid * s.d_in;
-    w.w_hid = off;
-    off += (s.depth - 1) * s.d_hid * s.d_hid;
-    w.w_out = off;
-    off += s.d_out * s.d_hid;
-    w.b_in = off;
-    off += s.d_hid;
-    w.b_hid = off;
-    off += (s.depth - 1) * s.d_hid;
-    w.b_out = off;
-    off += s.d_out;
-    w.total = off;
-    return w;
-}
 
 template <typename T>
 __global__ void __launch_bounds__(kThreadsMlp, 1)
@@ -430,10 +394,14 @@ int launch_mlp_bwd(const MlpShape &s, const MlpParams &p, const void *x, int64_t
                    int64_t go_stride, void *gx, int64_t gx_stride, void *dw_in, void *db_in, void *dw_hid, void *db_hid,
                    void *dw_out, void *db_out, float *workspace, int64_t rows, cudaStream_t stream) {
     const MlpSmem L = mlp_smem_layout(s, true);
-    if (int rc = set_smem_limit<T>(reinterpret_cast<const void *>(mlp_bwd_kernel<T>), L.total)) return rc;
     const MlpGradWorkspace W = grad_workspace_layout(s, workspace);
     if (int rc = cuda_status(cudaMemsetAsync(workspace, 0, sizeof(float) * W.total, stream), "cudaMemsetAsync(workspace)")) return rc;
-    if (rows > 0) {
+    const int tc = rows > 0 ? mlp_bwd_tc(s, p, x, x_stride, go, go_stride, gx, gx_stride, workspace, rows,
+                                         std::is_same<T, __half>::value ? TH_F16 : TH_BF16, stream)
+                            : kTcNotApplicable;
+    if (tc != kTcNotApplicable && tc != TH_OK) return tc;
+    if (rows > 0 && tc == kTcNotApplicable) {
+        if (int rc = set_smem_limit<T>(reinterpret_cast<const void *>(mlp_bwd_kernel<T>), L.total)) return rc;
         const long long tiles = (rows + kBwdRows - 1) / kBwdRows;
         const unsigned grid = static_cast<unsigned>(tiles < sm_count() ? tiles : sm_count());
         mlp_bwd_kernel<T><<<grid, kThreadsMlp, L.total, stream>>>(
@@ -474,6 +442,8 @@ extern "C" int th_mlp_fwd(const void *x_dev, int64_t x_stride, const void *w_in_
     if (!x_dev || !out_dev) return fail(TH_ERR_BAD_ARG, "null input or output");
     if (x_stride < d_in || out_stride < d_out) return fail(TH_ERR_BAD_ARG, "row stride smaller than the row");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // tcgen05 kernels first; the mma.sync kernels take what they do not cover
+    if (const int tc = mlp_fwd_tc(s, p, x_dev, x_stride, out_dev, out_stride, rows, dtype, st); tc != kTcNotApplicable) return tc;
     switch (dtype) {
         case TH_F16: return launch_mlp_fwd<__half>(s, p, x_dev, x_stride, out_dev, out_stride, rows, st);
         case TH_BF16: return launch_mlp_fwd<__nv_bfloat16>(s, p, x_dev, x_stride, out_dev, out_stride, rows, st);
