@@ -1,7 +1,8 @@
 // Fully fused MLP on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM).
 //
-// One CTA of 128 threads owns a 128-row tile at a time (M = 128 = the TMEM lanes); several CTAs
-// share an SM, so one CTA's epilogue overlaps another's MMAs.  Every operand tile lives in
+// One CTA of 256 threads owns a 128-row tile at a time (M = 128 = the TMEM lanes); several CTAs
+// share an SM, so one CTA's epilogue overlaps another's MMAs.  Warp w reads TMEM lanes
+// 32 * (w % 4) .. + 31 (thread = lane = tile row) and, of those rows, the column half w / 4.  Every operand tile lives in
 // shared memory in ONE layout: rows 128 bytes apart (64 16-bit features), 16-byte chunk c of
 // row r stored at chunk position c ^ (r & 7), tile base 1024-byte aligned.  That is the
 // canonical 128-byte-swizzle layout of the tensor core, and the same bytes can be described
@@ -15,10 +16,11 @@
 //   dgrad   : ACC[128 x in]  = DZ_l[128 x out] . W_l          A K-major, B MN-major
 //   wgrad   : DW_l[out x in] += DZ_l^T[out x 128] . ACT_l     A, B MN-major, M = 64
 //
-// Thread 0 issues the MMAs and commits them to an mbarrier; all 128 threads wait on it,
-// read their row of the accumulator with tcgen05.ld (thread = TMEM lane = tile row), apply
-// bias / activation / ReLU mask in registers and write the next operand tile straight back
-// to shared memory (fence.proxy.async before the tensor core reads it).  Weight gradients
+// Thread 0 issues the MMAs and commits them to an mbarrier; all 256 threads wait on it, read
+// their half row of the accumulator with tcgen05.ld in 8-column pieces (one piece = one 16-byte
+// chunk of the next operand tile), apply bias / activation / ReLU mask on packed 16-bit pairs
+// and write the next operand tile straight back to shared memory (fence.proxy.async before the
+// tensor core reads it).  Weight gradients
 // stay in TMEM columns for the whole life of the CTA (wgrad MMAs accumulate tile after tile
 // and are never waited on individually) and leave once, at the end, as red.global.add.f32.
 //
@@ -34,7 +36,9 @@
 namespace th {
 namespace {
 
-constexpr int kTcThreads = 128;
+constexpr int kGroups = 2;                    // column halves of a row, one per warpgroup
+constexpr int kTcThreads = 128 * kGroups;
+constexpr int kMaxChunks = 8 / kGroups;       // 16-byte chunks (8 columns) per thread at the widest layer
 constexpr int kTileRows = 128;
 constexpr int kTileBytes = kTileRows * 128;  // one operand tile: 128 rows x 128 B
 constexpr int kAccCols = 64;                 // TMEM columns of the forward / dgrad accumulator
@@ -43,13 +47,42 @@ constexpr int kWaitPolls = 1 << 22;
 
 __device__ int g_tc_status = 0;  // 0 = fine, 1 = an mbarrier wait ran out
 
+#ifdef TH_TC_TRACE
+// Development aid: cycle stamps of CTA 0 / thread 0 (never compiled into the shipped library).
+__device__ long long g_trace[4096];
+__device__ int g_trace_n = 0;
+#define TH_TRACE_BEGIN int trace_i = 0;
+#define TH_STAMP(tag)                                                             \
+    do {                                                                          \
+        if (blockIdx.x == 0 && threadIdx.x == 0 && trace_i < 2047) {              \
+            g_trace[2 * trace_i] = (tag);                                         \
+            g_trace[2 * trace_i + 1] = clock64();                                 \
+            ++trace_i;                                                            \
+        }                                                                         \
+    } while (0)
+#define TH_TRACE_END                                                              \
+    do {                                                                          \
+        if (blockIdx.x == 0 && threadIdx.x == 0) g_trace_n = trace_i;             \
+    } while (0)
+#else
+#define TH_TRACE_BEGIN
+#define TH_TRACE_END do { } while (0)
+#define TH_STAMP(tag) do { } while (0)
+#endif
+
 // ---- PTX wrappers ------------------------------------------------------------------------------
 
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-    // start address, LBO 0 (one 128-byte atom along the contiguous dimension), SBO 1024 B (8 rows),
-    // descriptor version 1, layout type 2 = 128-byte swizzle
-    return static_cast<uint64_t>((addr >> 4) & 0x3fff) | (static_cast<uint64_t>(1024 >> 4) << 32) |
-           (static_cast<uint64_t>(1) << 46) | (static_cast<uint64_t>(2) << 61);
+// Shared-memory matrix descriptor = {low word, high word}.  High word (constant for every tile here):
+// SBO 1024 B (8 rows of 128 B), descriptor version 1, layout type 2 = 128-byte swizzle.  Low word:
+// start address >> 4 in bits 0..13, LBO 0 (one 128-byte atom along the contiguous dimension).
+constexpr uint32_t kDescHigh = (1024u >> 4) | (1u << 14) | (2u << 29);
+
+__device__ __forceinline__ uint32_t desc_low(uint32_t addr) { return (addr >> 4) & 0x3fffu; }
+
+__device__ __forceinline__ uint64_t smem_desc(uint32_t low) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(low), "r"(kDescHigh));
+    return d;
 }
 
 // kind::f16 instruction descriptor: fp32 accumulate, A/B format 0 = f16 / 1 = bf16
@@ -66,6 +99,15 @@ __device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d),
         "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+
+// One lane of a converged warp.  MMAs are issued from warp-uniform code (all of warp 0 computes the
+// descriptors, one elected lane executes the instruction) so the descriptors live in uniform
+// registers, which is where tcgen05.mma takes them from.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}\n" : "=r"(pred));
+    return pred != 0;
 }
 
 __device__ __forceinline__ void mma_commit(uint32_t mbar) {
@@ -89,26 +131,72 @@ __device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity) {
     return done != 0;
 }
 
-// 16 consecutive accumulator columns of this thread's lane
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-        : "r"(taddr)
-        : "memory");
+// 8 consecutive accumulator columns of this thread's lane
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr)
+                 : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// COLS (16, 32, 48 or 64) accumulator columns of this thread's row, as floats
-template <int COLS>
-__device__ __forceinline__ void load_acc_row(uint32_t taddr, float (&v)[COLS]) {
-    uint32_t raw[COLS / 16][16];
+// This thread's `count` (<= kMaxChunks) 8-column pieces starting at piece `first`, all in flight together.
+__device__ __forceinline__ void load_pieces(uint32_t taddr, int first, int count, uint32_t (&raw)[kMaxChunks][8]) {
 #pragma unroll
-    for (int c = 0; c < COLS / 16; ++c) tmem_ld16(taddr + 16 * c, raw[c]);
+    for (int u = 0; u < kMaxChunks; ++u)
+        if (u < count) tmem_ld8(taddr + 8 * (first + u), raw[u]);
     tmem_ld_wait();
+}
+
+// ---- packed 16-bit arithmetic --------------------------------------------------------------------
+
+template <typename T>
+__device__ __forceinline__ uint32_t relu_pair(uint32_t v);
+template <>
+__device__ __forceinline__ uint32_t relu_pair<__half>(uint32_t v) {
+    const __half2 r = __hmax2(*reinterpret_cast<const __half2 *>(&v), __float2half2_rn(0.f));
+    return *reinterpret_cast<const uint32_t *>(&r);
+}
+template <>
+__device__ __forceinline__ uint32_t relu_pair<__nv_bfloat16>(uint32_t v) {
+    const __nv_bfloat162 r = __hmax2(*reinterpret_cast<const __nv_bfloat162 *>(&v), __float2bfloat162_rn(0.f));
+    return *reinterpret_cast<const uint32_t *>(&r);
+}
+
+// keep each 16-bit half of `grad` where the matching half of `post` is > 0
+template <typename T>
+__device__ __forceinline__ uint32_t keep_where_positive(uint32_t grad, uint32_t post);
+template <>
+__device__ __forceinline__ uint32_t keep_where_positive<__half>(uint32_t grad, uint32_t post) {
+    return grad & __hgt2_mask(*reinterpret_cast<const __half2 *>(&post), __float2half2_rn(0.f));
+}
+template <>
+__device__ __forceinline__ uint32_t keep_where_positive<__nv_bfloat16>(uint32_t grad, uint32_t post) {
+    return grad & __hgt2_mask(*reinterpret_cast<const __nv_bfloat162 *>(&post), __float2bfloat162_rn(0.f));
+}
+
+// 8 fp32 accumulator columns (+ bias) -> activation -> one 16-byte chunk of 16-bit values
+template <typename T, int ACT, bool BIAS>
+__device__ __forceinline__ uint4 finish_piece(const uint32_t (&raw)[8], const float *bias8) {
+    float v[8];
 #pragma unroll
-    for (int c = 0; c < COLS; ++c) v[c] = __uint_as_float(raw[c / 16][c % 16]);
+    for (int k = 0; k < 8; ++k) v[k] = __uint_as_float(raw[k]);
+    if constexpr (BIAS) {
+        const float4 b0 = *reinterpret_cast<const float4 *>(bias8), b1 = *reinterpret_cast<const float4 *>(bias8 + 4);
+        v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+        v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+    }
+    if constexpr (ACT == TH_ACT_SILU || ACT == TH_ACT_RELU2) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = activate(ACT, v[k]);
+    }
+    uint32_t w[4] = {pack_pair<T>(v[0], v[1]), pack_pair<T>(v[2], v[3]), pack_pair<T>(v[4], v[5]), pack_pair<T>(v[6], v[7])};
+    if constexpr (ACT == TH_ACT_RELU) {
+        // round, then clamp: the same value as clamp, then round
+#pragma unroll
+        for (int k = 0; k < 4; ++k) w[k] = relu_pair<T>(w[k]);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 // ---- operand tiles -----------------------------------------------------------------------------
@@ -117,28 +205,78 @@ __device__ __forceinline__ unsigned char *chunk_ptr(unsigned char *tile, int row
     return tile + row * 128 + ((chunk ^ (row & 7)) << 4);
 }
 
-// Rows [row0, row0 + 128) x cols [0, cols) of a row-major global matrix -> operand tile, zero padded
-// to `pad_cols`.  Coalesced: consecutive threads fetch consecutive 16-byte chunks.
-template <typename T>
-__device__ __forceinline__ void load_tile(unsigned char *tile, const T *src, long long stride, long long row0,
-                                          long long n_rows, int cols, int pad_cols, bool vector_ok) {
-    const int chunks = pad_cols / 8;
-    for (int id = threadIdx.x; id < kTileRows * chunks; id += kTcThreads) {
-        const int r = id / chunks, c = id - r * chunks;
-        const long long row = row0 + r;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (row < n_rows) {
-            const T *p = src + row * stride + 8 * c;
-            if (vector_ok) {
-                if (8 * c < cols) v = __ldcs(reinterpret_cast<const uint4 *>(p));
-            } else {
-                unsigned short e[8];
+__device__ __forceinline__ uint4 gather8(const unsigned short *p, int first_col, int cols) {
+    unsigned short e[8];
 #pragma unroll
-                for (int k = 0; k < 8; ++k) e[k] = (8 * c + k < cols) ? reinterpret_cast<const unsigned short *>(p)[k] : 0;
-                v = make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
+    for (int k = 0; k < 8; ++k) e[k] = (first_col + k < cols) ? p[k] : static_cast<unsigned short>(0);
+    return make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
+}
+
+// Rows [row0, row0 + 128) x cols [0, cols) of a row-major global matrix -> operand tile, zero padded
+// to `pad_cols`, in two steps so the global loads of the NEXT tile can be in flight while the
+// current one is computed: fetch_tile pulls this thread's 16-byte chunks into registers (coalesced:
+// consecutive threads fetch consecutive chunks), commit_tile writes them to their swizzled places.
+constexpr int kFetchIters = kTileRows * 8 / kTcThreads;
+struct TileRegs {
+    uint4 v[kFetchIters];
+};
+
+template <typename T>
+__device__ __forceinline__ void fetch_tile(TileRegs &t, const T *src, long long stride, long long row0, long long n_rows,
+                                           int cols, int pad_cols, bool vector_ok) {
+    const int chunks = pad_cols / 8;
+    const int total = kTileRows * chunks;
+#pragma unroll
+    for (int it = 0; it < kFetchIters; ++it) {
+        const int id = it * kTcThreads + threadIdx.x;
+        t.v[it] = make_uint4(0, 0, 0, 0);
+        if (id < total) {
+            const int r = id / chunks, c = id - r * chunks;
+            const long long row = row0 + r;
+            if (row < n_rows && 8 * c < cols) {
+                const T *p = src + row * stride + 8 * c;
+                t.v[it] = vector_ok ? __ldcs(reinterpret_cast<const uint4 *>(p))
+                                    : gather8(reinterpret_cast<const unsigned short *>(p), 8 * c, cols);
             }
         }
-        *reinterpret_cast<uint4 *>(chunk_ptr(tile, r, c)) = v;
+    }
+}
+
+// The same copy with cp.async: global -> swizzled shared memory without passing through registers
+// (rows past the end and padding columns are zero-filled by a zero source size).  Needs the
+// 16-byte-aligned layout (`vector_ok`); completion is awaited with async_tile_wait().
+template <typename T>
+__device__ __forceinline__ void async_tile_load(unsigned char *tile, const T *src, long long stride, long long row0,
+                                                long long n_rows, int cols, int pad_cols) {
+    const int chunks = pad_cols / 8;
+    const int total = kTileRows * chunks;
+#pragma unroll
+    for (int it = 0; it < kFetchIters; ++it) {
+        const int id = it * kTcThreads + threadIdx.x;
+        if (id < total) {
+            const int r = id / chunks, c = id - r * chunks;
+            const long long row = row0 + r;
+            const bool inside = row < n_rows && 8 * c < cols;
+            const T *p = inside ? src + row * stride + 8 * c : src;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(chunk_ptr(tile, r, c))), "l"(p),
+                         "r"(inside ? 16 : 0)
+                         : "memory");
+        }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void async_tile_wait() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+__device__ __forceinline__ void commit_tile(unsigned char *tile, const TileRegs &t, int pad_cols) {
+    const int chunks = pad_cols / 8;
+    const int total = kTileRows * chunks;
+#pragma unroll
+    for (int it = 0; it < kFetchIters; ++it) {
+        const int id = it * kTcThreads + threadIdx.x;
+        if (id < total) {
+            const int r = id / chunks, c = id - r * chunks;
+            *reinterpret_cast<uint4 *>(chunk_ptr(tile, r, c)) = t.v[it];
+        }
     }
 }
 
@@ -151,55 +289,33 @@ __device__ __forceinline__ void stage_weight_tile(unsigned char *tile, const T *
     for (int id = threadIdx.x; id < rows_pad * chunks; id += kTcThreads) {
         const int r = id / chunks, c = id - r * chunks;
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < rows) {
+        if (r < rows && 8 * c < cols) {
             const T *p = w + r * cols + 8 * c;
-            if (vector_ok) {
-                if (8 * c < cols) v = *reinterpret_cast<const uint4 *>(p);
-            } else {
-                unsigned short e[8];
-#pragma unroll
-                for (int k = 0; k < 8; ++k) e[k] = (8 * c + k < cols) ? reinterpret_cast<const unsigned short *>(p)[k] : 0;
-                v = make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
-            }
+            v = vector_ok ? *reinterpret_cast<const uint4 *>(p) : gather8(reinterpret_cast<const unsigned short *>(p), 8 * c, cols);
         }
         *reinterpret_cast<uint4 *>(chunk_ptr(tile, r, c)) = v;
     }
 }
 
-// This thread's row (COLS floats) -> 16-bit, into its row of an operand tile
-template <typename T, int COLS>
-__device__ __forceinline__ void store_row_to_tile(unsigned char *tile, int row, const float (&v)[COLS]) {
-#pragma unroll
-    for (int c = 0; c < COLS / 8; ++c) {
-        const uint4 packed = make_uint4(pack_pair<T>(v[8 * c], v[8 * c + 1]), pack_pair<T>(v[8 * c + 2], v[8 * c + 3]),
-                                        pack_pair<T>(v[8 * c + 4], v[8 * c + 5]), pack_pair<T>(v[8 * c + 6], v[8 * c + 7]));
-        *reinterpret_cast<uint4 *>(chunk_ptr(tile, row, c)) = packed;
-    }
-}
-
-// This thread's row (COLS floats) -> 16-bit, to a row-major global matrix
-template <typename T, int COLS>
-__device__ __forceinline__ void store_row_to_global(T *dst, int cols, const float (&v)[COLS], bool vector_ok) {
+// One 16-byte chunk (8 values) of this thread's row -> row-major global matrix
+template <typename T>
+__device__ __forceinline__ void store_chunk_to_global(T *row_ptr, int chunk, int cols, uint4 packed, bool vector_ok) {
+    if (8 * chunk >= cols) return;
     if (vector_ok) {
-#pragma unroll
-        for (int c = 0; c < COLS / 8; ++c) {
-            if (8 * c < cols) {
-                const uint4 packed = make_uint4(pack_pair<T>(v[8 * c], v[8 * c + 1]), pack_pair<T>(v[8 * c + 2], v[8 * c + 3]),
-                                                pack_pair<T>(v[8 * c + 4], v[8 * c + 5]), pack_pair<T>(v[8 * c + 6], v[8 * c + 7]));
-                __stcs(reinterpret_cast<uint4 *>(dst + 8 * c), packed);
-            }
-        }
+        __stcs(reinterpret_cast<uint4 *>(row_ptr + 8 * chunk), packed);
     } else {
+        const uint32_t w[4] = {packed.x, packed.y, packed.z, packed.w};
 #pragma unroll
-        for (int c = 0; c < COLS; ++c)
-            if (c < cols) dst[c] = from_float<T>(v[c]);
+        for (int k = 0; k < 8; ++k)
+            if (8 * chunk + k < cols)
+                reinterpret_cast<unsigned short *>(row_ptr)[8 * chunk + k] = static_cast<unsigned short>(w[k >> 1] >> (16 * (k & 1)));
     }
 }
 
 // ---- shared-memory plan ------------------------------------------------------------------------
 
 struct TcPlan {
-    int act_tiles;      // operand tiles for activations (1 forward, depth + 1 backward)
+    int act_tiles;      // operand tiles for activations (2 forward, depth + 1 backward)
     int dz_tiles;       // 0 forward, 2 backward
     int w_offset[3];    // byte offsets of W_in, W_hid[0], W_out tiles (after the activation / dz tiles)
     int w_hid_each;
@@ -210,7 +326,7 @@ struct TcPlan {
 
 __host__ __device__ inline TcPlan tc_plan(const MlpShape &s, bool backward) {
     TcPlan p{};
-    p.act_tiles = backward ? s.depth + 1 : 1;
+    p.act_tiles = backward ? s.depth + 1 : 2;  // forward: two tiles, alternating, so the next input can stream in
     p.dz_tiles = backward ? 2 : 0;
     int off = (p.act_tiles + p.dz_tiles) * kTileBytes;
     p.w_offset[0] = off;
@@ -288,42 +404,65 @@ __device__ __forceinline__ void cta_teardown(uint32_t tmem, uint32_t cols) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(cols) : "memory");
 }
 
-// Issue (thread 0 only) the K-loop of one GEMM.  a_step / b_step: bytes the operand's start address
-// advances per 16-deep K step (32 for a K-major operand, 2048 for an MN-major one).
-__device__ __forceinline__ void issue_gemm(uint32_t tmem_d, uint32_t a_addr, uint32_t a_step, uint32_t b_addr,
+// Issue the K-loop of one GEMM; called by all of warp 0, `leader` marks the elected lane.
+// a_step / b_step: bytes the operand's start address advances per 16-deep K step (32 for a K-major
+// operand, 2048 for an MN-major one).
+__device__ __forceinline__ void issue_gemm(bool leader, uint32_t tmem_d, uint32_t a_addr, uint32_t a_step, uint32_t b_addr,
                                            uint32_t b_step, int k_steps, uint32_t idesc, bool accumulate) {
-    for (int k = 0; k < k_steps; ++k)
-        mma_f16(tmem_d, smem_desc(a_addr + k * a_step), smem_desc(b_addr + k * b_step), idesc, (accumulate || k > 0) ? 1u : 0u);
+    uint32_t a_low = desc_low(a_addr), b_low = desc_low(b_addr);
+    uint32_t acc = accumulate ? 1u : 0u;
+    for (int k = 0; k < k_steps; ++k) {
+        if (leader) mma_f16(tmem_d, smem_desc(a_low), smem_desc(b_low), idesc, acc);
+        a_low += a_step >> 4;
+        b_low += b_step >> 4;
+        acc = 1u;
+    }
 }
 
-// bias + activation on this thread's accumulator row
-template <int COLS>
-__device__ __forceinline__ void bias_act(float (&v)[COLS], const float *bias, int act) {
-#pragma unroll
-    for (int c = 0; c < COLS; ++c) v[c] = activate(act, v[c] + bias[c]);
-}
+// Which rows / columns a thread looks after: TMEM lanes 32 * (warp % 4) .. + 31, column half warp / 4.
+struct Seat {
+    int row;            // tile row = TMEM lane
+    int group;          // column half
+    uint32_t lane_base; // lane field of the TMEM address
+    __device__ Seat() {
+        const int warp = threadIdx.x >> 5;
+        row = 32 * (warp & 3) + (threadIdx.x & 31);
+        group = warp >> 2;
+        lane_base = static_cast<uint32_t>(32 * (warp & 3)) << 16;
+    }
+};
 
 // ---- forward -----------------------------------------------------------------------------------
 
-template <typename T, int COLS>
-__device__ __forceinline__ void fwd_epilogue(uint32_t taddr, const float *bias, int act, unsigned char *next_tile,
-                                             int row) {
-    float v[COLS];
-    load_acc_row<COLS>(taddr, v);
-    bias_act<COLS>(v, bias, act);
-    store_row_to_tile<T, COLS>(next_tile, row, v);
+// A hidden layer's accumulator -> bias, activation, rounding -> this thread's chunks of the next operand tile
+template <typename T, int ACT, bool BIAS>
+__device__ __forceinline__ void hidden_epilogue(uint32_t taddr, const Seat &seat, int pad, const float *bias,
+                                                unsigned char *next_tile) {
+    const int count = pad / (8 * kGroups), first = seat.group * count;
+    uint32_t raw[kMaxChunks][8];
+    load_pieces(taddr, first, count, raw);
+#pragma unroll
+    for (int u = 0; u < kMaxChunks; ++u)
+        if (u < count)
+            *reinterpret_cast<uint4 *>(chunk_ptr(next_tile, seat.row, first + u)) =
+                finish_piece<T, ACT, BIAS>(raw[u], bias + 8 * (first + u));
 }
 
-template <typename T, int COLS>
-__device__ __forceinline__ void fwd_output(uint32_t taddr, const float *bias, T *dst, int cols, bool live, bool vector_ok) {
-    float v[COLS];
-    load_acc_row<COLS>(taddr, v);
-    bias_act<COLS>(v, bias, TH_ACT_NONE);
-    if (live) store_row_to_global<T, COLS>(dst, cols, v, vector_ok);
+template <typename T, bool BIAS>
+__device__ __forceinline__ void output_epilogue(uint32_t taddr, const Seat &seat, int pad, const float *bias, T *row_ptr,
+                                                int cols, bool live, bool vector_ok) {
+    const int count = pad / (8 * kGroups), first = seat.group * count;
+    uint32_t raw[kMaxChunks][8];
+    load_pieces(taddr, first, count, raw);
+#pragma unroll
+    for (int u = 0; u < kMaxChunks; ++u)
+        if (u < count && live)
+            store_chunk_to_global<T>(row_ptr, first + u, cols, finish_piece<T, TH_ACT_NONE, BIAS>(raw[u], bias + 8 * (first + u)),
+                                     vector_ok);
 }
 
-template <typename T>
-__global__ void __launch_bounds__(kTcThreads)
+template <typename T, int ACT, bool BIAS>
+__global__ void __launch_bounds__(kTcThreads, 3)
 mlp_fwd_tc_kernel(const MlpShape s, const MlpParams p, const T *__restrict__ x, long long x_stride, T *__restrict__ y,
                   long long y_stride, long long n_rows, int x_vec, int y_vec) {
     extern __shared__ unsigned char smem_raw[];
@@ -332,122 +471,153 @@ mlp_fwd_tc_kernel(const MlpShape s, const MlpParams p, const T *__restrict__ x, 
     __shared__ __align__(8) unsigned long long mbar;
     __shared__ int abort_flag;
     const TcPlan P = tc_plan(s, false);
-    constexpr int bf16 = sizeof(T) == 2 && !std::is_same<T, __half>::value;
+    constexpr int bf16 = std::is_same<T, __half>::value ? 0 : 1;
 
     if (threadIdx.x == 0) abort_flag = 0;
     stage_all_weights<T>(smem, P, s, p);
     const uint32_t tmem = cta_setup(&tmem_holder, &mbar, P.tmem_cols);
     const uint32_t bar = smem_addr(&mbar);
     const float *bias = reinterpret_cast<const float *>(smem + P.bias_offset);
-    unsigned char *act_tile = smem;
-    const uint32_t act_addr = smem_addr(act_tile);
-    const int row = threadIdx.x;
-    const uint32_t taddr = tmem + (static_cast<uint32_t>(row & ~31) << 16);  // this warp's 32 lanes
+    const Seat seat;
+    const uint32_t taddr = tmem + seat.lane_base;
     uint32_t phase = 0;
     const long long n_tiles = (n_rows + kTileRows - 1) / kTileRows;
+    TH_TRACE_BEGIN
 
-    for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    // Input tiles alternate between two buffers: while tile t runs through its layers in place in
+    // buffer t & 1, tile t + 1 streams into the other one.
+    auto start_input = [&](long long t, int b) {
+        unsigned char *dst = smem + b * kTileBytes;
+        if (x_vec) {
+            async_tile_load<T>(dst, x, x_stride, t * kTileRows, n_rows, s.d_in, s.ki);
+        } else {
+            TileRegs regs;
+            fetch_tile<T>(regs, x, x_stride, t * kTileRows, n_rows, s.d_in, s.ki, false);
+            commit_tile(dst, regs, s.ki);
+        }
+    };
+    int cur = 0;
+    if (static_cast<long long>(blockIdx.x) < n_tiles) start_input(blockIdx.x, 0);
+    for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, cur ^= 1) {
         const long long row0 = tile * kTileRows;
-        load_tile<T>(act_tile, x, x_stride, row0, n_rows, s.d_in, s.ki, x_vec);
+        unsigned char *act_tile = smem + cur * kTileBytes;
+        const uint32_t act_addr = smem_addr(act_tile);
+        TH_STAMP(100);
+        async_tile_wait();
+        TH_STAMP(101);
         fence_async_smem();
         tc_fence_before();
         __syncthreads();
+        TH_STAMP(102);
         if (abort_flag) break;
+        // the other buffer is free (its tile finished before the barrier above): start the next input
+        if (tile + gridDim.x < n_tiles) start_input(tile + gridDim.x, cur ^ 1);
         for (int l = 0; l <= s.depth; ++l) {
             const int in_pad = l == 0 ? s.ki : s.h;
             const int out_pad = l == s.depth ? s.no : s.h;
-            if (threadIdx.x == 0) {
+            TH_STAMP(9);
+            if (threadIdx.x < 32) {
+                const bool leader = elect_one();
                 tc_fence_after();
-                issue_gemm(tmem, act_addr, 32, smem_addr(weight_tile(smem, P, s, l)), 32, in_pad / 16,
+                TH_STAMP(10);
+                issue_gemm(leader, tmem, act_addr, 32, smem_addr(weight_tile(smem, P, s, l)), 32, in_pad / 16,
                            instr_desc(128, out_pad, bf16, 0, 0), false);
-                mma_commit(bar);
+                TH_STAMP(11);
+                if (leader) mma_commit(bar);
+                TH_STAMP(12);
+                __syncwarp();
             }
+            TH_STAMP(1);
             const bool ok = mbar_wait(bar, phase);
+            TH_STAMP(2);
             phase ^= 1;
             tc_fence_after();
             if (!ok) {
                 abort_flag = 1;
                 g_tc_status = 1;
             } else if (l < s.depth) {
-                const float *b = bias + l * kMaxDim;
-                switch (out_pad) {
-                    case 16: fwd_epilogue<T, 16>(taddr, b, s.act, act_tile, row); break;
-                    case 32: fwd_epilogue<T, 32>(taddr, b, s.act, act_tile, row); break;
-                    default: fwd_epilogue<T, 64>(taddr, b, s.act, act_tile, row); break;
-                }
+                hidden_epilogue<T, ACT, BIAS>(taddr, seat, out_pad, bias + l * kMaxDim, act_tile);
             } else {
-                const float *b = bias + l * kMaxDim;
-                const bool live = row0 + row < n_rows;
-                T *dst = y + (live ? row0 + row : 0) * y_stride;
-                switch (out_pad) {
-                    case 16: fwd_output<T, 16>(taddr, b, dst, s.d_out, live, y_vec); break;
-                    case 32: fwd_output<T, 32>(taddr, b, dst, s.d_out, live, y_vec); break;
-                    case 48: fwd_output<T, 48>(taddr, b, dst, s.d_out, live, y_vec); break;
-                    default: fwd_output<T, 64>(taddr, b, dst, s.d_out, live, y_vec); break;
-                }
+                const bool live = row0 + seat.row < n_rows;
+                output_epilogue<T, BIAS>(taddr, seat, out_pad, bias + l * kMaxDim, y + (live ? row0 + seat.row : 0) * y_stride,
+                                         s.d_out, live, y_vec);
             }
+            TH_STAMP(3);
             if (l < s.depth) {
                 fence_async_smem();
+                TH_STAMP(4);
                 tc_fence_before();
                 __syncthreads();
+                TH_STAMP(5);
                 if (abort_flag) break;
             }
         }
         tc_fence_before();
         if (abort_flag) break;
     }
+    TH_TRACE_END;
     cta_teardown(tmem, P.tmem_cols);
 }
 
 // ---- backward ----------------------------------------------------------------------------------
 
-// Epilogue of a recomputed forward layer: park the layer output in its own tile.
-// Epilogue of a dgrad: dz of the layer below = dy * act'(parked output of that layer).
-template <typename T, int COLS>
-__device__ __forceinline__ void bwd_dz_epilogue(uint32_t taddr, int act, const unsigned char *parked, unsigned char *dz_tile,
-                                                int row) {
-    float v[COLS];
-    load_acc_row<COLS>(taddr, v);
-    if (act == TH_ACT_RELU) {
+// Epilogue of a dgrad: dz of the layer below = dy * act'(that layer's parked output), rounded.
+template <typename T, int ACT>
+__device__ __forceinline__ void dz_epilogue(uint32_t taddr, const Seat &seat, int pad, unsigned char *parked,
+                                            unsigned char *dz_tile) {
+    const int count = pad / (8 * kGroups), first = seat.group * count;
+    uint32_t raw[kMaxChunks][8];
+    load_pieces(taddr, first, count, raw);
 #pragma unroll
-        for (int c = 0; c < COLS / 8; ++c) {
-            const uint4 a = *reinterpret_cast<const uint4 *>(chunk_ptr(const_cast<unsigned char *>(parked), row, c));
-            const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const float2 post = unpack_pair<T>(w[k]);
-                if (!(post.x > 0.f)) v[8 * c + 2 * k] = 0.f;
-                if (!(post.y > 0.f)) v[8 * c + 2 * k + 1] = 0.f;
+    for (int u = 0; u < kMaxChunks; ++u) {
+        if (u < count) {
+            uint4 g = finish_piece<T, TH_ACT_NONE, false>(raw[u], nullptr);
+            if constexpr (ACT == TH_ACT_RELU) {
+                const uint4 a = *reinterpret_cast<const uint4 *>(chunk_ptr(parked, seat.row, first + u));
+                g.x = keep_where_positive<T>(g.x, a.x);
+                g.y = keep_where_positive<T>(g.y, a.y);
+                g.z = keep_where_positive<T>(g.z, a.z);
+                g.w = keep_where_positive<T>(g.w, a.w);
             }
+            *reinterpret_cast<uint4 *>(chunk_ptr(dz_tile, seat.row, first + u)) = g;
         }
-    }
-    store_row_to_tile<T, COLS>(dz_tile, row, v);
-}
-
-template <typename T, int COLS>
-__device__ __forceinline__ void bwd_dx_epilogue(uint32_t taddr, T *dst, int cols, bool live, bool vector_ok) {
-    float v[COLS];
-    load_acc_row<COLS>(taddr, v);
-    if (live) store_row_to_global<T, COLS>(dst, cols, v, vector_ok);
-}
-
-// Flush one layer's weight-gradient accumulator (M = 64 layout: gradient row m sits in TMEM lane
-// 32 * (m / 16) + m % 16, so lanes 0..15 of each warp carry rows 16 * warp .. 16 * warp + 15).
-template <int COLS>
-__device__ __forceinline__ void flush_dw(uint32_t taddr, float *dst, int out_dim, int in_dim) {
-    float v[COLS];
-    load_acc_row<COLS>(taddr, v);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int m = 16 * warp + lane;
-    if (lane < 16 && m < out_dim) {
-#pragma unroll
-        for (int c = 0; c < COLS; ++c)
-            if (c < in_dim) atomicAdd(dst + m * in_dim + c, v[c]);
     }
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kTcThreads)
+__device__ __forceinline__ void dx_epilogue(uint32_t taddr, const Seat &seat, int pad, T *row_ptr, int cols, bool live,
+                                            bool vector_ok) {
+    const int count = pad / (8 * kGroups), first = seat.group * count;
+    uint32_t raw[kMaxChunks][8];
+    load_pieces(taddr, first, count, raw);
+#pragma unroll
+    for (int u = 0; u < kMaxChunks; ++u)
+        if (u < count && live)
+            store_chunk_to_global<T>(row_ptr, first + u, cols, finish_piece<T, TH_ACT_NONE, false>(raw[u], nullptr), vector_ok);
+}
+
+// Flush one layer's weight-gradient accumulator (M = 64 layout: gradient row m sits in TMEM lane
+// 32 * (m / 16) + m % 16, so lanes 0..15 of a warp's 32 carry rows 16 * (warp % 4) .. + 15).
+__device__ __forceinline__ void flush_dw(uint32_t taddr, const Seat &seat, int pad, float *dst, int out_dim, int in_dim) {
+    const int count = pad / (8 * kGroups), first = seat.group * count;
+    uint32_t raw[kMaxChunks][8];
+    load_pieces(taddr, first, count, raw);
+    const int lane = threadIdx.x & 31;
+    const int m = 16 * ((threadIdx.x >> 5) & 3) + lane;
+    if (lane < 16 && m < out_dim) {
+#pragma unroll
+        for (int u = 0; u < kMaxChunks; ++u)
+            if (u < count)
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const int c = 8 * (first + u) + k;
+                    if (c < in_dim) atomicAdd(dst + m * in_dim + c, __uint_as_float(raw[u][k]));
+                }
+    }
+}
+
+template <typename T, int ACT, int MINB>
+__global__ void __launch_bounds__(kTcThreads, MINB)
 mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const T *__restrict__ x, long long x_stride,
                   const T *__restrict__ go, long long go_stride, T *__restrict__ gx, long long gx_stride,
                   float *__restrict__ workspace, long long n_rows, int x_vec, int go_vec, int gx_vec) {
@@ -457,7 +627,7 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const T *__restrict__ x, 
     __shared__ __align__(8) unsigned long long mbar;
     __shared__ int abort_flag;
     const TcPlan P = tc_plan(s, true);
-    constexpr int bf16 = sizeof(T) == 2 && !std::is_same<T, __half>::value;
+    constexpr int bf16 = std::is_same<T, __half>::value ? 0 : 1;
 
     if (threadIdx.x == 0) abort_flag = 0;
     // operand tiles start out as zeros: columns a layer does not use are still read as MMA rows
@@ -467,31 +637,52 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const T *__restrict__ x, 
     const uint32_t tmem = cta_setup(&tmem_holder, &mbar, P.tmem_cols);
     const uint32_t bar = smem_addr(&mbar);
     unsigned char *dz_tiles = smem + P.act_tiles * kTileBytes;
-    const int row = threadIdx.x;
-    const uint32_t lane_base = static_cast<uint32_t>(row & ~31) << 16;
-    const uint32_t taddr = tmem + lane_base;
+    const Seat seat;
+    const uint32_t taddr = tmem + seat.lane_base;
     uint32_t phase = 0;
     bool first_tile = true;
     const long long n_tiles = (n_rows + kTileRows - 1) / kTileRows;
     auto act_tile = [&](int l) { return smem + l * kTileBytes; };
     auto dw_col = [&](int l) { return kAccCols + (l == 0 ? 0 : s.ki + (l - 1) * s.h); };
 
+    // With one CTA per SM (MINB == 1: shared memory bound, registers to spare) the next tile's inputs
+    // are fetched into registers while the current tile computes; with two CTAs per SM the other
+    // CTA covers the latency and the registers are needed elsewhere.
+    constexpr bool kPrefetch = MINB == 1;
+    TileRegs x_next, go_next;
+    if (kPrefetch && static_cast<long long>(blockIdx.x) < n_tiles) {
+        fetch_tile<T>(x_next, x, x_stride, static_cast<long long>(blockIdx.x) * kTileRows, n_rows, s.d_in, s.ki, x_vec);
+        fetch_tile<T>(go_next, go, go_stride, static_cast<long long>(blockIdx.x) * kTileRows, n_rows, s.d_out, s.no, go_vec);
+    }
     for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         const long long row0 = tile * kTileRows;
         // ---- phase 1: recompute the forward, parking every layer input ----
-        load_tile<T>(act_tile(0), x, x_stride, row0, n_rows, s.d_in, s.ki, x_vec);
-        load_tile<T>(dz_tiles, go, go_stride, row0, n_rows, s.d_out, s.no, go_vec);  // dz of the output layer = grad_out
+        if (kPrefetch) {
+            commit_tile(act_tile(0), x_next, s.ki);
+            commit_tile(dz_tiles, go_next, s.no);  // dz of the output layer = grad_out
+        } else {
+            fetch_tile<T>(x_next, x, x_stride, row0, n_rows, s.d_in, s.ki, x_vec);
+            commit_tile(act_tile(0), x_next, s.ki);
+            fetch_tile<T>(x_next, go, go_stride, row0, n_rows, s.d_out, s.no, go_vec);
+            commit_tile(dz_tiles, x_next, s.no);
+        }
         fence_async_smem();
         tc_fence_before();
         __syncthreads();
         if (abort_flag) break;
+        if (kPrefetch && tile + gridDim.x < n_tiles) {
+            fetch_tile<T>(x_next, x, x_stride, (tile + gridDim.x) * kTileRows, n_rows, s.d_in, s.ki, x_vec);
+            fetch_tile<T>(go_next, go, go_stride, (tile + gridDim.x) * kTileRows, n_rows, s.d_out, s.no, go_vec);
+        }
         for (int l = 0; l < s.depth; ++l) {
             const int in_pad = l == 0 ? s.ki : s.h;
-            if (threadIdx.x == 0) {
+            if (threadIdx.x < 32) {
+                const bool leader = elect_one();
                 tc_fence_after();
-                issue_gemm(tmem, smem_addr(act_tile(l)), 32, smem_addr(weight_tile(smem, P, s, l)), 32, in_pad / 16,
+                issue_gemm(leader, tmem, smem_addr(act_tile(l)), 32, smem_addr(weight_tile(smem, P, s, l)), 32, in_pad / 16,
                            instr_desc(128, s.h, bf16, 0, 0), false);
-                mma_commit(bar);
+                if (leader) mma_commit(bar);
+                __syncwarp();
             }
             const bool ok = mbar_wait(bar, phase);
             phase ^= 1;
@@ -500,12 +691,7 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const T *__restrict__ x, 
                 abort_flag = 1;
                 g_tc_status = 1;
             } else {
-                const float *b = reinterpret_cast<const float *>(smem + P.bias_offset) + l * kMaxDim;
-                switch (s.h) {
-                    case 16: fwd_epilogue<T, 16>(taddr, b, s.act, act_tile(l + 1), row); break;
-                    case 32: fwd_epilogue<T, 32>(taddr, b, s.act, act_tile(l + 1), row); break;
-                    default: fwd_epilogue<T, 64>(taddr, b, s.act, act_tile(l + 1), row); break;
-                }
+                hidden_epilogue<T, ACT, false>(taddr, seat, s.h, nullptr, act_tile(l + 1));
             }
             fence_async_smem();
             tc_fence_before();
@@ -521,16 +707,19 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const T *__restrict__ x, 
             const int out_pad = l == s.depth ? s.no : s.h;
             unsigned char *dz = dz_tiles + buf * kTileBytes;
             const bool need_dgrad = l > 0 || gx != nullptr;
-            if (threadIdx.x == 0) {
+            if (threadIdx.x < 32) {
+                const bool leader = elect_one();
                 tc_fence_after();
-                // wgrad: DW_l[out x in] += DZ^T . ACT_l over the tile's 128 rows (both operands MN-major)
-                issue_gemm(tmem + dw_col(l), smem_addr(dz), 2048, smem_addr(act_tile(l)), 2048, kTileRows / 16,
-                           instr_desc(64, in_pad, bf16, 1, 1), !first_tile);
-                // dgrad: ACC[128 x in] = DZ . W_l (A K-major over the layer's outputs, W_l tile MN-major)
+                // dgrad first (the epilogue waits for it): ACC[128 x in] = DZ . W_l (A K-major over the
+                // layer's outputs, W_l tile MN-major)
                 if (need_dgrad)
-                    issue_gemm(tmem, smem_addr(dz), 32, smem_addr(weight_tile(smem, P, s, l)), 2048, out_pad / 16,
+                    issue_gemm(leader, tmem, smem_addr(dz), 32, smem_addr(weight_tile(smem, P, s, l)), 2048, out_pad / 16,
                                instr_desc(128, in_pad, bf16, 0, 1), false);
-                mma_commit(bar);
+                // wgrad: DW_l[out x in] += DZ^T . ACT_l over the tile's 128 rows (both operands MN-major)
+                issue_gemm(leader, tmem + dw_col(l), smem_addr(dz), 2048, smem_addr(act_tile(l)), 2048, kTileRows / 16,
+                           instr_desc(64, in_pad, bf16, 1, 1), !first_tile);
+                if (leader) mma_commit(bar);
+                __syncwarp();
             }
             const bool ok = mbar_wait(bar, phase);
             phase ^= 1;
@@ -540,21 +729,10 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const T *__restrict__ x, 
                 g_tc_status = 1;
             } else if (l > 0) {
                 // in_pad == s.h here: the layer below produced ACT_l
-                unsigned char *next = dz_tiles + (buf ^ 1) * kTileBytes;
-                switch (s.h) {
-                    case 16: bwd_dz_epilogue<T, 16>(taddr, s.act, act_tile(l), next, row); break;
-                    case 32: bwd_dz_epilogue<T, 32>(taddr, s.act, act_tile(l), next, row); break;
-                    default: bwd_dz_epilogue<T, 64>(taddr, s.act, act_tile(l), next, row); break;
-                }
+                dz_epilogue<T, ACT>(taddr, seat, in_pad, act_tile(l), dz_tiles + (buf ^ 1) * kTileBytes);
             } else if (gx != nullptr) {
-                const bool live = row0 + row < n_rows;
-                T *dst = gx + (live ? row0 + row : 0) * gx_stride;
-                switch (in_pad) {
-                    case 16: bwd_dx_epilogue<T, 16>(taddr, dst, s.d_in, live, gx_vec); break;
-                    case 32: bwd_dx_epilogue<T, 32>(taddr, dst, s.d_in, live, gx_vec); break;
-                    case 48: bwd_dx_epilogue<T, 48>(taddr, dst, s.d_in, live, gx_vec); break;
-                    default: bwd_dx_epilogue<T, 64>(taddr, dst, s.d_in, live, gx_vec); break;
-                }
+                const bool live = row0 + seat.row < n_rows;
+                dx_epilogue<T>(taddr, seat, in_pad, gx + (live ? row0 + seat.row : 0) * gx_stride, s.d_in, live, gx_vec);
             }
             fence_async_smem();
             tc_fence_before();
@@ -574,13 +752,7 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const T *__restrict__ x, 
             const int in_pad = l == 0 ? s.ki : s.h;
             const int in_dim = l == 0 ? s.d_in : s.d_hid, out_dim = l == s.depth ? s.d_out : s.d_hid;
             float *dst = W.base + (l == 0 ? W.w_in : (l == s.depth ? W.w_out : W.w_hid + (l - 1) * s.d_hid * s.d_hid));
-            const uint32_t t = taddr + dw_col(l);
-            switch (in_pad) {
-                case 16: flush_dw<16>(t, dst, out_dim, in_dim); break;
-                case 32: flush_dw<32>(t, dst, out_dim, in_dim); break;
-                case 48: flush_dw<48>(t, dst, out_dim, in_dim); break;
-                default: flush_dw<64>(t, dst, out_dim, in_dim); break;
-            }
+            flush_dw(taddr + dw_col(l), seat, in_pad, dst, out_dim, in_dim);
         }
     }
     cta_teardown(tmem, P.tmem_cols);
@@ -615,40 +787,69 @@ bool tc_disabled() {
     return off;
 }
 
-template <typename T>
-int launch_fwd(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, void *y, int64_t y_stride,
-               int64_t rows, cudaStream_t stream) {
+template <typename T, int ACT, bool BIAS>
+int launch_fwd_t(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, void *y, int64_t y_stride,
+                 int64_t rows, cudaStream_t stream) {
     const TcPlan P = tc_plan(s, false);
     int ctas = 0;
     const int smem = occupancy_plan(P, &ctas);
     if (ctas < 1) return kTcNotApplicable;
-    if (int rc = cuda_status(cudaFuncSetAttribute(mlp_fwd_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+    auto kernel = mlp_fwd_tc_kernel<T, ACT, BIAS>;
+    if (int rc = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
                              "cudaFuncSetAttribute(mlp_fwd_tc_kernel)")) return rc;
     const long long tiles = (rows + kTileRows - 1) / kTileRows;
     const long long cap = static_cast<long long>(sm_count()) * ctas;
-    mlp_fwd_tc_kernel<T><<<static_cast<unsigned>(tiles < cap ? tiles : cap), kTcThreads, smem, stream>>>(
+    kernel<<<static_cast<unsigned>(tiles < cap ? tiles : cap), kTcThreads, smem, stream>>>(
         s, p, static_cast<const T *>(x), x_stride, static_cast<T *>(y), y_stride, rows, rows_vector_ok(x, x_stride, s.d_in),
         rows_vector_ok(y, y_stride, s.d_out));
     return cuda_status(cudaGetLastError(), "mlp_fwd_tc_kernel launch");
 }
 
+template <typename T, bool BIAS>
+int launch_fwd_act(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, void *y, int64_t y_stride,
+                   int64_t rows, cudaStream_t stream) {
+    switch (s.act) {
+        case TH_ACT_RELU: return launch_fwd_t<T, TH_ACT_RELU, BIAS>(s, p, x, x_stride, y, y_stride, rows, stream);
+        case TH_ACT_SILU: return launch_fwd_t<T, TH_ACT_SILU, BIAS>(s, p, x, x_stride, y, y_stride, rows, stream);
+        case TH_ACT_RELU2: return launch_fwd_t<T, TH_ACT_RELU2, BIAS>(s, p, x, x_stride, y, y_stride, rows, stream);
+        default: return launch_fwd_t<T, TH_ACT_NONE, BIAS>(s, p, x, x_stride, y, y_stride, rows, stream);
+    }
+}
+
 template <typename T>
-int launch_bwd(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, const void *go, int64_t go_stride,
-               void *gx, int64_t gx_stride, float *workspace, int64_t rows, cudaStream_t stream) {
+int launch_fwd(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, void *y, int64_t y_stride,
+               int64_t rows, cudaStream_t stream) {
+    return s.has_bias ? launch_fwd_act<T, true>(s, p, x, x_stride, y, y_stride, rows, stream)
+                      : launch_fwd_act<T, false>(s, p, x, x_stride, y, y_stride, rows, stream);
+}
+
+template <typename T, int ACT>
+int launch_bwd_t(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, const void *go, int64_t go_stride,
+                 void *gx, int64_t gx_stride, float *workspace, int64_t rows, cudaStream_t stream) {
     const TcPlan P = tc_plan(s, true);
     if (P.tmem_cols > 512) return kTcNotApplicable;
     int ctas = 0;
     const int smem = occupancy_plan(P, &ctas);
     if (ctas < 1) return kTcNotApplicable;
-    if (int rc = cuda_status(cudaFuncSetAttribute(mlp_bwd_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+    // one CTA per SM (shared memory bound): let it keep its prefetched tiles in registers
+    auto kernel = ctas >= 2 ? mlp_bwd_tc_kernel<T, ACT, 2> : mlp_bwd_tc_kernel<T, ACT, 1>;
+    if (int rc = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
                              "cudaFuncSetAttribute(mlp_bwd_tc_kernel)")) return rc;
     const long long tiles = (rows + kTileRows - 1) / kTileRows;
     const long long cap = static_cast<long long>(sm_count()) * ctas;
-    mlp_bwd_tc_kernel<T><<<static_cast<unsigned>(tiles < cap ? tiles : cap), kTcThreads, smem, stream>>>(
+    kernel<<<static_cast<unsigned>(tiles < cap ? tiles : cap), kTcThreads, smem, stream>>>(
         s, p, static_cast<const T *>(x), x_stride, static_cast<const T *>(go), go_stride, static_cast<T *>(gx), gx_stride,
         workspace, rows, rows_vector_ok(x, x_stride, s.d_in), rows_vector_ok(go, go_stride, s.d_out),
         gx ? rows_vector_ok(gx, gx_stride, s.d_in) : 0);
     return cuda_status(cudaGetLastError(), "mlp_bwd_tc_kernel launch");
+}
+
+template <typename T>
+int launch_bwd(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, const void *go, int64_t go_stride,
+               void *gx, int64_t gx_stride, float *workspace, int64_t rows, cudaStream_t stream) {
+    return s.act == TH_ACT_RELU
+               ? launch_bwd_t<T, TH_ACT_RELU>(s, p, x, x_stride, go, go_stride, gx, gx_stride, workspace, rows, stream)
+               : launch_bwd_t<T, TH_ACT_NONE>(s, p, x, x_stride, go, go_stride, gx, gx_stride, workspace, rows, stream);
 }
 
 }  // namespace
@@ -678,6 +879,18 @@ int mlp_bwd_tc(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_s
 }
 
 }  // namespace th
+
+#ifdef TH_TC_TRACE
+extern "C" int th_tc_trace_read(long long *out_host, int max_pairs) {
+    int n = 0;
+    cudaMemcpyFromSymbol(&n, th::g_trace_n, sizeof(int));
+    if (n > max_pairs) n = max_pairs;
+    cudaMemcpyFromSymbol(out_host, th::g_trace, sizeof(long long) * 2 * n);
+    int zero = 0;
+    cudaMemcpyToSymbol(th::g_trace_n, &zero, sizeof(int));
+    return n;
+}
+#endif
 
 // Device-side status of the tcgen05 kernels: 0 = fine, 1 = a bounded wait ran out.  Synchronises.
 extern "C" int th_mlp_tc_status(void) {
