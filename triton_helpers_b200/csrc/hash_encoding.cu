@@ -393,7 +393,8 @@ hash_fwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, const
     const long long i = static_cast<long long>(blockIdx.x) * kPoints + (threadIdx.x >> 1);
     T *out_row = out + (live ? i : 0) * out_stride;
 
-    for (int lg = level_begin; lg < level_end; lg += LG) {
+    // gridDim.y CTAs share a point tile and take every gridDim.y-th level group each
+    for (int lg = level_begin + LG * blockIdx.y; lg < level_end; lg += LG * gridDim.y) {
         float acc[kCount];
         float e[LG][kSide][F];
         float w[LG][kSide];
@@ -464,7 +465,8 @@ hash_bwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, const
     const T *go_row = grad_out + (live ? i : 0) * go_stride;
     const unsigned lane = threadIdx.x & 31u;
 
-    for (int lg = level_begin; lg < level_end; lg += LG) {
+    // gridDim.y CTAs share a point tile and take every gridDim.y-th level group each
+    for (int lg = level_begin + LG * blockIdx.y; lg < level_end; lg += LG * gridDim.y) {
         float go[LG * F];
         if (live) {
             load_elems_checked<T, LG * F>(go_row + lg * F, go, vector_ok);  // both lanes of a pair: one broadcast load
@@ -615,10 +617,24 @@ int pick_level_group(int level_begin, int level_end, int n_feats) {
     return 1;
 }
 
+// Grid: x = point tiles (128 points each); y = how many CTAs split the level groups of a tile.
+// Large batches fill the GPU with point tiles alone (y = 1: coordinates are read once per point);
+// small ones (a few waves or less) would leave every thread with a serial chain of level groups and
+// most of the machine idle, so their level groups are spread over y CTAs instead.
+dim3 point_level_grid(int64_t n, int l0, int l1, int levels_per_group) {
+    const long long tiles = (n + kThreads / 2 - 1) / (kThreads / 2);
+    const int groups = (l1 - l0) / levels_per_group;
+    int split = 1;
+    const long long resident = static_cast<long long>(sm_count()) * 8;  // CTAs the GPU holds at once
+    while (split < groups && tiles * split < 4 * resident) split *= 2;
+    if (split > groups) split = groups;
+    return dim3(static_cast<unsigned>(tiles), static_cast<unsigned>(split), 1);
+}
+
 template <typename T, int D, int F>
 int launch_fwd(const LevelParams &P, const CoordView &cv, const void *table, void *out, int64_t out_stride,
                int64_t n, int l0, int l1, cudaStream_t stream) {
-    const unsigned grid = static_cast<unsigned>((n + kThreads / 2 - 1) / (kThreads / 2));
+    const dim3 grid = point_level_grid(n, l0, l1, pick_level_group(l0, l1, F));
     const int vec = aligned_to(out, 16) && (out_stride * sizeof(T)) % 16 == 0;
     const T *tb = static_cast<const T *>(table);
     T *o = static_cast<T *>(out);
@@ -633,7 +649,7 @@ int launch_fwd(const LevelParams &P, const CoordView &cv, const void *table, voi
 template <typename T, int D, int F>
 int launch_bwd(const LevelParams &P, const CoordView &cv, const void *go, int64_t go_stride, void *grad_table,
                int64_t n, int l0, int l1, cudaStream_t stream) {
-    const unsigned grid = static_cast<unsigned>((n + kThreads / 2 - 1) / (kThreads / 2));
+    const dim3 grid = point_level_grid(n, l0, l1, pick_level_group(l0, l1, F));
     const int vec = aligned_to(go, 16) && (go_stride * sizeof(T)) % 16 == 0;
     const T *g = static_cast<const T *>(go);
     T *gt = static_cast<T *>(grad_table);
