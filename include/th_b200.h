@@ -140,6 +140,11 @@ int th_mlp_fwd(const void *x_dev, int64_t x_stride, const void *w_in_dev, const 
  * No counterpart in the reference. */
 int th_mlp_tc_status(void);
 
+/* 1 when the tensor-core MLP kernels can load their weights by TMA in this process (the driver
+ * exposes cuTensorMapEncodeTiled), 0 when they stage them with plain loads.  No counterpart in the
+ * reference. */
+int th_mlp_tma_available(void);
+
 /* Bytes of fp32 scratch th_mlp_bwd needs (one float per parameter); -1 for an unsupported shape. */
 int64_t th_mlp_workspace_bytes(int d_in, int d_hidden, int d_out, int depth);
 

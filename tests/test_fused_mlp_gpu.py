@@ -250,6 +250,8 @@ def test_tensor_core_kernels_never_timed_out():
     from triton_helpers_b200 import _lib
 
     assert _lib.lib().th_mlp_tc_status() == 0
+    # and their weights came in by TMA (tensor maps could be built on this driver)
+    assert _lib.lib().th_mlp_tma_available() == 1
 
 
 def test_mma_sync_kernels_still_pass_when_selected():

@@ -48,6 +48,7 @@ SIGNATURES = {
     ),
     "th_mlp_workspace_bytes": (c_int64, [c_int, c_int, c_int, c_int]),
     "th_mlp_tc_status": (c_int, []),
+    "th_mlp_tma_available": (c_int, []),
     "th_mlp_bwd": (
         c_int,
         [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,

@@ -24,13 +24,22 @@
 // stay in TMEM columns for the whole life of the CTA (wgrad MMAs accumulate tile after tile
 // and are never waited on individually) and leave once, at the end, as red.global.add.f32.
 //
+// Weights reach shared memory by TMA (cp.async.bulk.tensor.2d, one box per layer, 128-byte swizzle:
+// the box lands directly in the operand-tile layout, zero filled where a layer is narrower than its
+// padded tile); arrays TMA cannot describe (inner dimension not a multiple of 8 elements) are staged
+// with plain loads instead.  No multicast: every CTA loads its own copy.
+//
 // Every wait is bounded: a stuck mbarrier sets a device-side status word and the CTA frees its
 // TMEM and returns.  tcgen05.alloc cannot block for good because the launcher sizes shared
 // memory so that the CTAs resident on one SM never ask for more than its 512 TMEM columns.
 #include "mlp_shape.cuh"
 #include "mma_tiles.cuh"
 
+#include <cuda.h>  // CUtensorMap and its enums only; the driver entry point is looked up at run time
+
 #include <cstdlib>
+#include <cstring>
+#include <mutex>
 #include <type_traits>
 
 namespace th {
@@ -353,14 +362,43 @@ __device__ __forceinline__ unsigned char *weight_tile(unsigned char *smem, const
     return smem + P.w_offset[1] + (l - 1) * P.w_hid_each;
 }
 
+// Tensor maps of the three weight arrays (see make_weight_maps): 2-D, 16-bit elements, box = 64
+// columns x one layer's rows, 128-byte swizzle, zero fill outside the array.  A TMA box lands in
+// shared memory exactly in the operand-tile layout (row pitch 128 B, chunk ^ (row & 7)).
+struct WeightMaps {
+    CUtensorMap w_in, w_hid, w_out;
+};
+
+__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint32_t mbar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_addr(smem_dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(mbar)
+        : "memory");
+}
+
+// All weight tiles of the network by TMA: thread 0 arms the barrier with the byte count and issues
+// one box per layer; everybody waits (bounded) for the bytes to land.  Returns false on a timeout.
+__device__ bool tma_stage_weights(unsigned char *smem, const TcPlan &P, const MlpShape &s, const WeightMaps &maps,
+                                  unsigned long long *wbar) {
+    const uint32_t bar = smem_addr(wbar);
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(1u) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t bytes = static_cast<uint32_t>((s.h + (s.depth - 1) * s.h + s.no) * 128);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+        tma_load_2d(smem + P.w_offset[0], &maps.w_in, 0, 0, bar);
+        for (int i = 0; i < s.depth - 1; ++i) tma_load_2d(smem + P.w_offset[1] + i * P.w_hid_each, &maps.w_hid, 0, i * s.d_hid, bar);
+        tma_load_2d(smem + P.w_offset[2], &maps.w_out, 0, 0, bar);
+    }
+    return mbar_wait(bar, 0);
+}
+
 template <typename T>
-__device__ void stage_all_weights(unsigned char *smem, const TcPlan &P, const MlpShape &s, const MlpParams &p) {
-    stage_weight_tile<T>(smem + P.w_offset[0], static_cast<const T *>(p.w_in), s.d_hid, s.d_in, s.h, s.ki);
-    for (int i = 0; i < s.depth - 1; ++i)
-        stage_weight_tile<T>(smem + P.w_offset[1] + i * P.w_hid_each,
-                             static_cast<const T *>(p.w_hid) + static_cast<size_t>(i) * s.d_hid * s.d_hid, s.d_hid,
-                             s.d_hid, s.h, s.h);
-    stage_weight_tile<T>(smem + P.w_offset[2], static_cast<const T *>(p.w_out), s.d_out, s.d_hid, s.no, s.h);
+__device__ void stage_biases(unsigned char *smem, const TcPlan &P, const MlpShape &s, const MlpParams &p) {
     float *bias = reinterpret_cast<float *>(smem + P.bias_offset);
     for (int e = threadIdx.x; e < (s.depth + 1) * kMaxDim; e += kTcThreads) {
         const int layer = e / kMaxDim, c = e % kMaxDim;
@@ -376,6 +414,18 @@ __device__ void stage_all_weights(unsigned char *smem, const TcPlan &P, const Ml
         }
         bias[e] = v;
     }
+}
+
+// Weights without TMA (inner dimension not a multiple of 8 elements, or a misaligned pointer): plain
+// loads and swizzled stores by all threads.
+template <typename T>
+__device__ void stage_all_weights(unsigned char *smem, const TcPlan &P, const MlpShape &s, const MlpParams &p) {
+    stage_weight_tile<T>(smem + P.w_offset[0], static_cast<const T *>(p.w_in), s.d_hid, s.d_in, s.h, s.ki);
+    for (int i = 0; i < s.depth - 1; ++i)
+        stage_weight_tile<T>(smem + P.w_offset[1] + i * P.w_hid_each,
+                             static_cast<const T *>(p.w_hid) + static_cast<size_t>(i) * s.d_hid * s.d_hid, s.d_hid,
+                             s.d_hid, s.h, s.h);
+    stage_weight_tile<T>(smem + P.w_offset[2], static_cast<const T *>(p.w_out), s.d_out, s.d_hid, s.no, s.h);
 }
 
 // TMEM allocation by warp 0, mbarrier init by thread 0, then a CTA-wide hand-over.
@@ -463,8 +513,9 @@ __device__ __forceinline__ void output_epilogue(uint32_t taddr, const Seat &seat
 
 template <typename T, int ACT, bool BIAS>
 __global__ void __launch_bounds__(kTcThreads, 3)
-mlp_fwd_tc_kernel(const MlpShape s, const MlpParams p, const T *__restrict__ x, long long x_stride, T *__restrict__ y,
-                  long long y_stride, long long n_rows, int x_vec, int y_vec) {
+mlp_fwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ WeightMaps maps, const int use_tma,
+                  const T *__restrict__ x, long long x_stride, T *__restrict__ y, long long y_stride, long long n_rows,
+                  int x_vec, int y_vec) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint32_t tmem_holder;
@@ -473,9 +524,18 @@ mlp_fwd_tc_kernel(const MlpShape s, const MlpParams p, const T *__restrict__ x, 
     const TcPlan P = tc_plan(s, false);
     constexpr int bf16 = std::is_same<T, __half>::value ? 0 : 1;
 
+    __shared__ __align__(8) unsigned long long wbar;
     if (threadIdx.x == 0) abort_flag = 0;
-    stage_all_weights<T>(smem, P, s, p);
+    stage_biases<T>(smem, P, s, p);
+    bool weights_ok = true;
+    if (use_tma) weights_ok = tma_stage_weights(smem, P, s, maps, &wbar);
+    else stage_all_weights<T>(smem, P, s, p);
     const uint32_t tmem = cta_setup(&tmem_holder, &mbar, P.tmem_cols);
+    if (!weights_ok) {  // the bytes never arrived: report and leave (after the barrier inside cta_setup)
+        abort_flag = 1;
+        g_tc_status = 1;
+    }
+    __syncthreads();
     const uint32_t bar = smem_addr(&mbar);
     const float *bias = reinterpret_cast<const float *>(smem + P.bias_offset);
     const Seat seat;
@@ -618,7 +678,8 @@ __device__ __forceinline__ void flush_dw(uint32_t taddr, const Seat &seat, int p
 
 template <typename T, int ACT, int MINB>
 __global__ void __launch_bounds__(kTcThreads, MINB)
-mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const T *__restrict__ x, long long x_stride,
+mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ WeightMaps maps, const int use_tma,
+                  const T *__restrict__ x, long long x_stride,
                   const T *__restrict__ go, long long go_stride, T *__restrict__ gx, long long gx_stride,
                   float *__restrict__ workspace, long long n_rows, int x_vec, int go_vec, int gx_vec) {
     extern __shared__ unsigned char smem_raw[];
@@ -626,6 +687,7 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const T *__restrict__ x, 
     __shared__ uint32_t tmem_holder;
     __shared__ __align__(8) unsigned long long mbar;
     __shared__ int abort_flag;
+    __shared__ __align__(8) unsigned long long wbar;
     const TcPlan P = tc_plan(s, true);
     constexpr int bf16 = std::is_same<T, __half>::value ? 0 : 1;
 
@@ -633,8 +695,16 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const T *__restrict__ x, 
     // operand tiles start out as zeros: columns a layer does not use are still read as MMA rows
     for (int e = threadIdx.x; e < (P.act_tiles + P.dz_tiles) * kTileBytes / 16; e += kTcThreads)
         reinterpret_cast<uint4 *>(smem)[e] = make_uint4(0, 0, 0, 0);
-    stage_all_weights<T>(smem, P, s, p);
+    stage_biases<T>(smem, P, s, p);
+    bool weights_ok = true;
+    if (use_tma) weights_ok = tma_stage_weights(smem, P, s, maps, &wbar);
+    else stage_all_weights<T>(smem, P, s, p);
     const uint32_t tmem = cta_setup(&tmem_holder, &mbar, P.tmem_cols);
+    if (!weights_ok) {
+        abort_flag = 1;
+        g_tc_status = 1;
+    }
+    __syncthreads();
     const uint32_t bar = smem_addr(&mbar);
     unsigned char *dz_tiles = smem + P.act_tiles * kTileBytes;
     const Seat seat;
@@ -779,6 +849,60 @@ int occupancy_plan(const TcPlan &P, int *ctas_per_sm) {
     return need > floor_bytes ? need : floor_bytes;
 }
 
+// ---- tensor maps for the weights ---------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled through the runtime's driver-entry-point lookup (no link against libcuda).
+EncodeTiledFn encode_tiled_fn() {
+    static std::mutex guard;
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    std::lock_guard<std::mutex> lock(guard);
+    if (!tried) {
+        tried = true;
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult status;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &status) == cudaSuccess &&
+            status == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// One map per weight array: [rows][cols] 16-bit row-major, box = 64 columns x box_rows rows.
+bool make_map(CUtensorMap *map, const void *base, int rows, int cols, int box_rows) {
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode || !base || cols % 8 != 0 || !aligned_to(base, 16)) return false;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+    const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t elem[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void *>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Returns 1 when all three maps could be built (then the kernels load the weights by TMA), else 0.
+int make_weight_maps(WeightMaps &maps, const MlpShape &s, const MlpParams &p) {
+    memset(&maps, 0, sizeof(maps));
+    static const bool off = [] {
+        const char *v = getenv("TH_MLP_NO_TMA");
+        return v && v[0] == '1';
+    }();
+    if (off) return 0;
+    if (!make_map(&maps.w_in, p.w_in, s.d_hid, s.d_in, s.h)) return 0;
+    if (s.depth > 1) {
+        if (!make_map(&maps.w_hid, p.w_hid, (s.depth - 1) * s.d_hid, s.d_hid, s.h)) return 0;
+    } else {
+        maps.w_hid = maps.w_in;  // never used
+    }
+    if (!make_map(&maps.w_out, p.w_out, s.d_out, s.d_hid, s.no)) return 0;
+    return 1;
+}
+
 bool tc_disabled() {
     static const bool off = [] {
         const char *v = getenv("TH_MLP_LEGACY");
@@ -799,9 +923,11 @@ int launch_fwd_t(const MlpShape &s, const MlpParams &p, const void *x, int64_t x
                              "cudaFuncSetAttribute(mlp_fwd_tc_kernel)")) return rc;
     const long long tiles = (rows + kTileRows - 1) / kTileRows;
     const long long cap = static_cast<long long>(sm_count()) * ctas;
+    WeightMaps maps;
+    const int use_tma = make_weight_maps(maps, s, p);
     kernel<<<static_cast<unsigned>(tiles < cap ? tiles : cap), kTcThreads, smem, stream>>>(
-        s, p, static_cast<const T *>(x), x_stride, static_cast<T *>(y), y_stride, rows, rows_vector_ok(x, x_stride, s.d_in),
-        rows_vector_ok(y, y_stride, s.d_out));
+        s, p, maps, use_tma, static_cast<const T *>(x), x_stride, static_cast<T *>(y), y_stride, rows,
+        rows_vector_ok(x, x_stride, s.d_in), rows_vector_ok(y, y_stride, s.d_out));
     return cuda_status(cudaGetLastError(), "mlp_fwd_tc_kernel launch");
 }
 
@@ -837,8 +963,10 @@ int launch_bwd_t(const MlpShape &s, const MlpParams &p, const void *x, int64_t x
                              "cudaFuncSetAttribute(mlp_bwd_tc_kernel)")) return rc;
     const long long tiles = (rows + kTileRows - 1) / kTileRows;
     const long long cap = static_cast<long long>(sm_count()) * ctas;
+    WeightMaps maps;
+    const int use_tma = make_weight_maps(maps, s, p);
     kernel<<<static_cast<unsigned>(tiles < cap ? tiles : cap), kTcThreads, smem, stream>>>(
-        s, p, static_cast<const T *>(x), x_stride, static_cast<const T *>(go), go_stride, static_cast<T *>(gx), gx_stride,
+        s, p, maps, use_tma, static_cast<const T *>(x), x_stride, static_cast<const T *>(go), go_stride, static_cast<T *>(gx), gx_stride,
         workspace, rows, rows_vector_ok(x, x_stride, s.d_in), rows_vector_ok(go, go_stride, s.d_out),
         gx ? rows_vector_ok(gx, gx_stride, s.d_in) : 0);
     return cuda_status(cudaGetLastError(), "mlp_bwd_tc_kernel launch");
@@ -891,6 +1019,10 @@ extern "C" int th_tc_trace_read(long long *out_host, int max_pairs) {
     return n;
 }
 #endif
+
+// 1 when tensor maps can be built in this process (the driver exposes cuTensorMapEncodeTiled), i.e.
+// when the tensor-core MLP kernels load their weights by TMA; 0 when they fall back to plain loads.
+extern "C" int th_mlp_tma_available(void) { return th::encode_tiled_fn() != nullptr ? 1 : 0; }
 
 // Device-side status of the tcgen05 kernels: 0 = fine, 1 = a bounded wait ran out.  Synchronises.
 extern "C" int th_mlp_tc_status(void) {
