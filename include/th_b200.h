@@ -203,6 +203,10 @@ int th_rev_fwd(const void *x_dev, int64_t x_stride, const void *w_f1_dev, const 
                const void *b_g1_dev, const void *b_g2_dev, void *out_dev, int64_t out_stride, int64_t rows,
                int d_model, int d_hidden, int blocks, int activation, int dtype, void *stream);
 
+/* Device-side status word of the reversible tensor-core kernels (0 = fine, 1 = a bounded wait ran
+ * out and results are invalid).  Synchronises the device. */
+int th_rev_tc_status(void);
+
 /* Bytes of fp32 scratch th_rev_bwd needs for `rows` rows: one private copy of all weight-gradient
  * accumulators per resident CTA (about 0.5 MB per CTA for 8 blocks of 64 x 64). */
 int64_t th_rev_workspace_bytes(int64_t rows, int d_model, int d_hidden, int blocks);

@@ -67,6 +67,7 @@ SIGNATURES = {
         [c_void_p, c_int64] + [c_void_p] * 8 + [c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p],
     ),
     "th_rev_workspace_bytes": (c_int64, [c_int64, c_int, c_int, c_int]),
+    "th_rev_tc_status": (c_int, []),
     "th_rev_bwd": (
         c_int,
         [c_void_p, c_int64] + [c_void_p] * 8 + [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64]

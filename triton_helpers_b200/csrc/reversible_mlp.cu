@@ -17,7 +17,10 @@
 // on the way.  Per block and 128-row tile the four weight gradients are formed cooperatively
 // (K = 128 rows) and added into CTA-private fp32 accumulators that live in global memory and
 // stay L2 resident (no atomics: one CTA owns one copy); a reduction kernel sums the copies.
+#include "rev_shape.cuh"
 #include "mma_tiles.cuh"
+
+#include <type_traits>
 
 namespace th {
 namespace {
@@ -25,19 +28,6 @@ namespace {
 constexpr int kRevWarps = 8;
 constexpr int kRevThreads = kRevWarps * 32;
 constexpr int kRevRows = kRevWarps * 16;  // rows per CTA tile
-constexpr int kMatFloats = 8 * 512;       // fragment-native fp32 slots of one weight-gradient matrix
-
-struct RevShape {
-    int half, hid;  // width of x1 / x2, hidden width of F and G (multiples of 16, <= 64)
-    int blocks;
-    int act;
-    int has_bias;
-};
-
-struct RevParams {
-    const void *w_f1, *w_f2, *w_g1, *w_g2;  // (blocks*hid, half), (blocks*half, hid), ...
-    const void *b_f1, *b_f2, *b_g1, *b_g2;  // (blocks, hid), (blocks, half), ...
-};
 
 struct RevSmem {
     int w_stage;       // bytes of one ring stage: [w_f1 | w_f2 | w_g1 | w_g2]
@@ -241,11 +231,6 @@ __device__ __forceinline__ void tile_bias_grad(const T *tile, int width, float *
     atomicAdd(dst + col, sum);
 }
 
-// Per-CTA accumulator layout: [block][matrix 0..3][kMatFloats] then [block][4][64] bias sums.
-__host__ __device__ inline size_t rev_cta_floats(const RevShape &s) {
-    return static_cast<size_t>(s.blocks) * 4 * kMatFloats + static_cast<size_t>(s.blocks) * 4 * kMaxDim;
-}
-
 template <typename T>
 __global__ void __launch_bounds__(kRevThreads, 1)
 rev_bwd_kernel(const RevShape s, const RevParams p, const T *__restrict__ y, long long y_stride,
@@ -445,6 +430,11 @@ int launch_rev_bwd(const RevShape &s, const RevParams &p, const void *y, int64_t
     const int grid = rev_grid(rows);
     const size_t bytes = sizeof(float) * rev_cta_floats(s) * grid;
     if (int rc = cuda_status(cudaMemsetAsync(workspace, 0, bytes, stream), "cudaMemsetAsync(workspace)")) return rc;
+    // tensor-core kernels first (they also reduce and write the gradients); mma.sync kernels otherwise
+    const int tc = rows > 0 ? rev_bwd_tc(s, p, y, y_stride, go, go_stride, gx, gx_stride, x_rec, xr_stride, dw, workspace, grid,
+                                         rows, std::is_same<T, __half>::value ? TH_F16 : TH_BF16, stream)
+                            : kRevTcNotApplicable;
+    if (tc != kRevTcNotApplicable) return tc;
     if (rows > 0) {
         rev_bwd_kernel<T><<<grid, kRevThreads, L.total, stream>>>(
             s, p, static_cast<const T *>(y), y_stride, static_cast<const T *>(go), go_stride, static_cast<T *>(gx),
@@ -484,6 +474,7 @@ extern "C" int th_rev_fwd(const void *x_dev, int64_t x_stride, const void *w_f1_
     if (int rc = check_rows(x_dev, x_stride, d_model, "input")) return rc;
     if (int rc = check_rows(out_dev, out_stride, d_model, "output")) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (const int tc = rev_fwd_tc(s, p, x_dev, x_stride, out_dev, out_stride, rows, dtype, st); tc != kRevTcNotApplicable) return tc;
     switch (dtype) {
         case TH_F16: return launch_rev_fwd<__half>(s, p, x_dev, x_stride, out_dev, out_stride, rows, st);
         case TH_BF16: return launch_rev_fwd<__nv_bfloat16>(s, p, x_dev, x_stride, out_dev, out_stride, rows, st);
