@@ -18,7 +18,7 @@
 // Weights (4 matrices per block) stream block by block through a two-stage cp.async ring in the
 // operand-tile layout; the same tile is read K-major by the forward GEMMs and MN-major by dgrad.
 // Weight gradients of a (tile, block, branch) leave TMEM straight into the CTA's private fp32
-// accumulator in global memory (plain read-modify-write, one owner per copy, L2 resident); a
+// accumulator in global memory (vector red.global.add, one owner per copy, L2 resident); a
 // reduction kernel sums the copies.  The backward pass needs all 512 TMEM columns, so one CTA
 // per SM; the forward pass needs 192 (256 allocated), two CTAs per SM.
 //
@@ -244,17 +244,17 @@ __device__ __forceinline__ void flush_dw_private(uint32_t taddr, const Seat &sea
     const int lane = threadIdx.x & 31;
     const int m = 16 * ((threadIdx.x >> 5) & 3) + lane;
     if (lane < 16 && m < out_dim) {
+        // fire-and-forget vector reductions: no round trip to wait for, and nobody else touches this copy
 #pragma unroll
         for (int u = 0; u < kMaxChunks; ++u) {
             if (u < count) {
-                float4 *q = reinterpret_cast<float4 *>(dst + m * 64 + 8 * (first + u));
-                float4 a = q[0], b = q[1];
-                a.x += __uint_as_float(raw[u][0]); a.y += __uint_as_float(raw[u][1]);
-                a.z += __uint_as_float(raw[u][2]); a.w += __uint_as_float(raw[u][3]);
-                b.x += __uint_as_float(raw[u][4]); b.y += __uint_as_float(raw[u][5]);
-                b.z += __uint_as_float(raw[u][6]); b.w += __uint_as_float(raw[u][7]);
-                q[0] = a;
-                q[1] = b;
+                float *q = dst + m * 64 + 8 * (first + u);
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(q + 4 * h),
+                                 "f"(__uint_as_float(raw[u][4 * h])), "f"(__uint_as_float(raw[u][4 * h + 1])),
+                                 "f"(__uint_as_float(raw[u][4 * h + 2])), "f"(__uint_as_float(raw[u][4 * h + 3]))
+                                 : "memory");
             }
         }
     }
