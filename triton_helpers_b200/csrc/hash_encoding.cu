@@ -31,6 +31,7 @@ namespace th {
 namespace {
 
 constexpr int kThreads = 256;
+constexpr uint32_t kAggregateMaxRes = 64;  // backward: finest grid on which warp aggregation is attempted
 
 struct LevelParams {
     uint32_t res[TH_MAX_LEVELS];
@@ -484,20 +485,27 @@ hash_bwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, const
             side_indices<D>(cell, P, level, side, idx);
             T *base = grad_table + P.offset[level] * F;
 
-            // Lanes on the same side of the same cell share all their rows.  The key packs the exact
-            // cell (20 bits per axis) and the side; dead lanes and cells too large to pack get a key
-            // nobody else has.
-            unsigned long long key = 0;
-            bool packable = live;
+            // Lanes on the same side of the same cell share all their rows.  Looking for them costs a
+            // match.any per level, which only pays on coarse grids: with res > kAggregateMaxRes even
+            // tightly clustered points (sigma = 0.02) put two of a warp's 16 points in one cell less than
+            // once in a hundred levels, so finer levels go straight to the atomics.  The key packs the
+            // exact cell (20 bits per axis) and the side; dead lanes and cells too large to pack get a
+            // key nobody else has.
+            bool shared_cell = false;
+            unsigned peers = 1u << lane;
+            if (P.res[level] <= kAggregateMaxRes) {
+                unsigned long long key = 0;
+                bool packable = live;
 #pragma unroll
-            for (int d = 0; d < D; ++d) {
-                packable = packable && cell[d] < (1u << 20);
-                key = (key << 20) | (cell[d] & 0xfffffu);
+                for (int d = 0; d < D; ++d) {
+                    packable = packable && cell[d] < (1u << 20);
+                    key = (key << 20) | (cell[d] & 0xfffffu);
+                }
+                key = (key << 1) | static_cast<unsigned>(side);
+                if (!packable) key = (1ull << 63) | lane;
+                peers = __match_any_sync(0xffffffffu, key);
+                shared_cell = __any_sync(0xffffffffu, (peers & (peers - 1)) != 0);
             }
-            key = (key << 1) | static_cast<unsigned>(side);
-            if (!packable) key = (1ull << 63) | lane;
-            const unsigned peers = __match_any_sync(0xffffffffu, key);
-            const bool shared_cell = __any_sync(0xffffffffu, (peers & (peers - 1)) != 0);
 
             if (!shared_cell) {
                 if (live) {
