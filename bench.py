@@ -32,6 +32,13 @@ import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
 METRIC = "fwd+bwd points/sec (hash-enc + fused MLP)"
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu captures summarised under
+# profiles/ (hash_bwd_kernel_cfg3.md, hash_fwd_kernel_cfg3.md, mlp_tc_kernels_cfg3.md), all taken on
+# the full cfg 3 workload.  Other workloads have no capture yet: traffic is reported as null there.
+NCU_TRAFFIC_BYTES = {
+    "train_step": {"th_hash_bwd": 193.5e6, "th_hash_fwd": 131.4e6, "th_mlp_bwd": 292.4e6, "th_mlp_fwd": 170.7e6},
+}
 L2_BYTES = 126 * 1024 * 1024
 
 
@@ -405,7 +412,7 @@ def main():
     else:
         achieved, peak, unit = amount * (args.steps / calls) / per_launch_s / 1e12, peaks["tflops"], "TFLOP/s"
     roofline = {"kernel": top, "bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
-                "traffic": None, "peak_source": peaks["source"], "algorithmic_per_launch": amount * (args.steps / calls),
+                "traffic": NCU_TRAFFIC_BYTES.get(args.workload, {}).get(top), "peak_source": peaks["source"], "algorithmic_per_launch": amount * (args.steps / calls),
                 "ms_per_launch": per_launch_s * 1e3}  # fmt: skip
 
     e2e = None
