@@ -211,8 +211,26 @@ def test_argument_checks_match_the_reference():
     with pytest.raises(ValueError):
         x2 = torch.randn(2, 8, device="cuda", dtype=dtype)
         fully_fused_mlp(x2, p["w_in"], p["b_in"], p["w_out"], p["b_out"])
-    with pytest.raises(TypeError, match="float16 or bfloat16"):
-        fully_fused_mlp(x.float(), *(None if v is None else v.float() for v in (p["w_in"], p["b_in"], p["w_out"], p["b_out"])))
+    with pytest.raises(TypeError, match="share one dtype"):
+        fully_fused_mlp(x.float(), p["w_in"], p["b_in"], p["w_out"], p["b_out"])
+
+
+@pytest.mark.parametrize("depth", [1, 3])
+def test_float32_tensors_like_the_reference(depth):
+    # reference test_forward_shallow / test_backward_shallow with dtype=float32: tol 1e-3 forward, 1e-2 backward
+    p32 = make_params(8, 16, 4, depth, torch.float32)
+    torch.manual_seed(0)
+    x = torch.randn(2, 2, 8)
+    go = torch.randn(2, 2, 4)
+    want, got = run_both(x, p32, go, "relu")
+    assert got[0].dtype == torch.float32 and got[1].dtype == torch.float32
+    torch.testing.assert_close(got[0].cpu(), want[0], rtol=1e-3, atol=1e-3)
+    assert_all_close(want, got, tol=1e-2)
+    # depth >= 4 in float32: forward works, backward is refused as in the reference
+    p_deep = {k: (None if v is None else v.cuda().requires_grad_(True)) for k, v in make_params(8, 16, 4, 4, torch.float32).items()}
+    y = fully_fused_mlp(x.cuda(), p_deep["w_in"], p_deep["b_in"], p_deep["w_out"], p_deep["b_out"], p_deep["w_hid"], p_deep["b_hid"])
+    with pytest.raises(AssertionError, match="FP32 backward not supported"):
+        y.sum().backward()
 
 
 @pytest.mark.parametrize("depth", [1, 4, 8])

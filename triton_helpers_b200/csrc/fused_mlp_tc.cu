@@ -260,12 +260,9 @@ mlp_fwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
                 __syncwarp();
             }
             TH_STAMP(1);
-            const bool ok = mbar_wait(bar, phase);
+            const bool ok = cta_wait_mma(bar, phase, &abort_flag);
             TH_STAMP(2);
-            phase ^= 1;
-            tc_fence_after();
             if (!ok) {
-                abort_flag = 1;
                 g_tc_status = 1;
             } else if (l < s.depth) {
                 hidden_epilogue<T, ACT, BIAS>(taddr, seat, out_pad, bias + l * kMaxDim, act_tile);
@@ -426,11 +423,8 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
                 if (leader) mma_commit(bar);
                 __syncwarp();
             }
-            const bool ok = mbar_wait(bar, phase);
-            phase ^= 1;
-            tc_fence_after();
+            const bool ok = cta_wait_mma(bar, phase, &abort_flag);
             if (!ok) {
-                abort_flag = 1;
                 g_tc_status = 1;
             } else {
                 hidden_epilogue<T, ACT, false>(taddr, seat, s.h, nullptr, act_tile(l + 1));
@@ -463,11 +457,8 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
                 if (leader) mma_commit(bar);
                 __syncwarp();
             }
-            const bool ok = mbar_wait(bar, phase);
-            phase ^= 1;
-            tc_fence_after();
+            const bool ok = cta_wait_mma(bar, phase, &abort_flag);
             if (!ok) {
-                abort_flag = 1;
                 g_tc_status = 1;
             } else if (l > 0) {
                 // in_pad == s.h here: the layer below produced ACT_l

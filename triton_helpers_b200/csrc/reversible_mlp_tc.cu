@@ -128,15 +128,12 @@ __device__ __forceinline__ void stream_epilogue(uint32_t taddr, const Seat &seat
     if constexpr (BIAS) tmem_st_wait();
 }
 
-__device__ __forceinline__ bool commit_and_wait(bool leader, uint32_t bar, uint32_t &phase) {
+__device__ __forceinline__ bool commit_and_wait(bool leader, uint32_t bar, uint32_t &phase, int *abort_flag) {
     if (threadIdx.x < 32) {
         if (leader) mma_commit(bar);
         __syncwarp();
     }
-    const bool ok = mbar_wait(bar, phase);
-    phase ^= 1;
-    tc_fence_after();
-    return ok;
+    return cta_wait_mma(bar, phase, abort_flag);
 }
 
 __device__ __forceinline__ void publish_tiles() {
@@ -203,7 +200,7 @@ rev_fwd_tc_kernel(const RevShape s, const RevParams p, const T *__restrict__ x, 
                     tc_fence_after();
                     issue_gemm(leader, tmem + kFwdHid, smem_addr(u_tile), 32, w1, 32, s.half / 16, idesc_hid, false);
                 }
-                if (!commit_and_wait(leader, bar, phase)) abort_flag = 1;
+                commit_and_wait(leader, bar, phase, &abort_flag);
                 {
                     const int count = s.hid / (8 * kGroups), first = seat.group * count;
                     uint32_t raw[kMaxChunks][8];
@@ -220,7 +217,7 @@ rev_fwd_tc_kernel(const RevShape s, const RevParams p, const T *__restrict__ x, 
                     tc_fence_after();
                     issue_gemm(leader, tmem + out_col, smem_addr(h_tile), 32, w2, 32, s.hid / 16, idesc_half, true);
                 }
-                if (!commit_and_wait(leader, bar, phase)) abort_flag = 1;
+                commit_and_wait(leader, bar, phase, &abort_flag);
                 // the updated stream: rounded copy for the next branch, and the output after the last block
                 const bool last = k == s.blocks - 1;
                 stream_epilogue<T, BIAS>(taddr + out_col, seat, s.half, bias + (2 * branch + 1) * kMaxDim, u_tile,
@@ -330,7 +327,7 @@ rev_bwd_tc_kernel(const RevShape s, const RevParams p, const T *__restrict__ y, 
                     issue_gemm(leader, tmem + kZ, smem_addr(u_tile), 32, w1, 32, s.half / 16, id_z, false);
                     issue_gemm(leader, tmem + kDH, smem_addr(dy_tile), 32, w2, 2048, s.half / 16, id_dh, false);
                 }
-                if (!commit_and_wait(leader, bar, phase)) abort_flag = 1;
+                commit_and_wait(leader, bar, phase, &abort_flag);
                 {
                     const int count = s.hid / (8 * kGroups), first = seat.group * count;
                     uint32_t zraw[kMaxChunks][8], draw[kMaxChunks][8];
@@ -362,7 +359,7 @@ rev_bwd_tc_kernel(const RevShape s, const RevParams p, const T *__restrict__ y, 
                     issue_gemm(leader, tmem + kDW2, smem_addr(dy_tile), 2048, smem_addr(h_tile), 2048, kTileRows / 16, id_dw2, false);
                     issue_gemm(leader, tmem + kDW1, smem_addr(dz_tile), 2048, smem_addr(u_tile), 2048, kTileRows / 16, id_dw1, false);
                 }
-                if (!commit_and_wait(leader, bar, phase)) abort_flag = 1;
+                commit_and_wait(leader, bar, phase, &abort_flag);
                 // next pass: its input is the stream just reconstructed, its output gradient the one just updated
                 stream_epilogue<T, false>(taddr + out_col, seat, s.half, nullptr, u_tile, nullptr, false);
                 stream_epilogue<T, false>(taddr + in_d_col, seat, s.half, nullptr, dy_tile, nullptr, false);

@@ -115,6 +115,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity) {
     return done != 0;
 }
 
+// CTA-wide wait for the MMAs committed to `mbar`: only warp 0 polls the mbarrier (bounded); the other
+// warps park at the CTA barrier, which costs no issue slots while they wait.  Returns false (for
+// every thread alike) when the wait ran out; `abort_flag` lives in shared memory.
+__device__ __forceinline__ bool cta_wait_mma(uint32_t mbar, uint32_t &phase, int *abort_flag) {
+    if (threadIdx.x < 32) {
+        if (!mbar_wait(mbar, phase)) *abort_flag = 1;
+        tc_fence_after();
+        tc_fence_before();
+    }
+    phase ^= 1;
+    __syncthreads();
+    tc_fence_after();
+    return *abort_flag == 0;
+}
+
 // 8 consecutive accumulator columns of this thread's lane
 __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"

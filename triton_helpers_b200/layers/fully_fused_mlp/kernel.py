@@ -7,9 +7,11 @@ Triton launches are replaced by ``th_mlp_fwd`` / ``th_mlp_bwd`` of ``libth_b200.
 
 Differences a caller can observe:
 
-* float16 and bfloat16 only.  The reference also takes float32 tensors (``tl.dot`` in TF32);
-  here a float32 call raises ``TypeError`` (under autocast everything is cast to float16 first,
-  as in the reference, so module use is unaffected).
+* float32 tensors are accepted like in the reference, whose ``tl.dot`` then runs in TF32 (10-bit
+  operand mantissa, float32 accumulation).  Here they are rounded to float16 (the same 10-bit
+  mantissa, float32 accumulation) for the tensor cores and the results are returned in float32;
+  values beyond the float16 range (|v| > 65504) overflow, which TF32 would not.  As in the
+  reference, a float32 backward pass is refused for depth >= 4 (reference :576).
 * ``fp16_acc`` is accepted and ignored: accumulation is always float32.
 * biases may be ``None`` (all of them) for a bias-free network; the reference requires tensors.
 * the Triton device functions the reference re-exports (``feedforward`` ...) do not exist.
@@ -41,8 +43,8 @@ def _check_dtype(*tensors: Optional[Tensor]) -> torch.dtype:
     if len(dtypes) != 1:
         raise TypeError(f"input and parameters must share one dtype, got {dtypes}")
     (dtype,) = dtypes
-    if dtype not in (torch.float16, torch.bfloat16):
-        raise TypeError(f"fused MLP kernels take float16 or bfloat16 tensors, got {dtype}")
+    if dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        raise TypeError(f"fused MLP kernels take float16, bfloat16 or float32 tensors, got {dtype}")
     return dtype
 
 
@@ -90,7 +92,12 @@ class _fully_fused_mlp(Function):
         )
 
         device = _lib.require_cuda(x, w_in, b_in, w_out, b_out, w_hid, b_hid)
-        dtype = _check_dtype(x, w_in, b_in, w_out, b_out, w_hid, b_hid)
+        io_dtype = _check_dtype(x, w_in, b_in, w_out, b_out, w_hid, b_hid)
+        dtype = torch.float16 if io_dtype == torch.float32 else io_dtype  # float32: float16 operands, fp32 accumulate
+        if io_dtype == torch.float32:
+            x, w_in, w_out = x.to(dtype), w_in.to(dtype), w_out.to(dtype)
+            w_hid = None if w_hid is None else w_hid.to(dtype)
+            b_in, b_out, b_hid = (None if b is None else b.to(dtype) for b in (b_in, b_out, b_hid))
         x = _rows_view(x)
         w_in, w_out = w_in.contiguous(), w_out.contiguous()
         w_hid = None if w_hid is None else w_hid.contiguous()
@@ -111,13 +118,15 @@ class _fully_fused_mlp(Function):
         ctx.activation = activation
         ctx.fp16_acc = fp16_acc
         ctx.depth = depth
-        return o
+        ctx.io_dtype = io_dtype
+        return o if io_dtype == dtype else o.to(io_dtype)
 
     @staticmethod
     @torch.amp.custom_bwd(device_type="cuda")
     @torch.no_grad()
     def backward(ctx, do: Tensor):
         x, w_in, b_in, w_out, b_out, w_hid, b_hid = ctx.saved_tensors
+        assert ctx.io_dtype != torch.float32 or ctx.depth < 4, "FP32 backward not supported for depth >= 4"
         B, L, D_in = x.shape
         D_hidden, _ = w_in.shape
         D_out, _ = w_out.shape
@@ -146,6 +155,9 @@ class _fully_fused_mlp(Function):
                 ),
                 "th_mlp_bwd",
             )  # fmt: skip
+        if ctx.io_dtype != dtype:
+            cast = lambda t: None if t is None else t.to(ctx.io_dtype)  # noqa: E731
+            dx, dw_in, db_in, dw_out, db_out, dw_hid, db_hid = map(cast, (dx, dw_in, db_in, dw_out, db_out, dw_hid, db_hid))
         return dx, dw_in, db_in, dw_out, db_out, dw_hid, db_hid, None, None
 
 
