@@ -320,6 +320,47 @@ def cpu_training_step_rate(steps, warmup, points):
     return points * steps / dt, threads, dt / steps * 1e3
 
 
+def cpu_operator_rate(workload):
+    r"""(units/s, threads, sample text) of the CPU oracle of one operator's forward + backward, bounded sample."""
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    if workload in HASH_CFG:
+        from oracle import hash_encoding as oracle
+
+        c = HASH_CFG[workload]
+        n = 2**16
+        kw = dict(table_cap=c["cap"], levels=16, n_min=16, n_max=c["n_max"])
+        rows = sum(oracle.level_rows(16, c["cap"], 3, 16, c["n_max"]))
+        table = (torch.rand(rows, c["feats"], generator=g) * 2 - 1) * 1e-4
+        x, go = torch.rand(n, 3, generator=g), torch.randn(n, 16 * c["feats"], generator=g)
+        fn = lambda: (oracle.encode(x, table, **kw), oracle.encode_backward(x, go, table, **kw))  # noqa: E731
+        sample = f"{n} uniform points, float32 table of {rows} rows (the reference's CPU path restated in oracle/)"
+    elif workload == "mlp":
+        from oracle import fused_mlp as oracle
+
+        n = 2**18
+        lin = lambda o, i: (torch.rand(o, i, generator=g) * 2 - 1) / i**0.5  # noqa: E731
+        w = (lin(64, 32), lin(16, 64), lin(192, 64))
+        x, go = torch.randn(1, n, 32, generator=g), torch.randn(1, n, 16, generator=g) * 1e-2
+        fn = lambda: oracle.forward_backward(x, w[0], None, w[1], None, w[2], None, go)  # noqa: E731
+        sample = f"{n} rows, float32 F.linear chain with autograd (oracle/)"
+    else:
+        from oracle import reversible_mlp as oracle
+
+        n = 2**16
+        w = tuple((torch.rand(512, 64, generator=g) * 2 - 1) / 8 for _ in range(4))
+        x, go = torch.randn(n, 128, generator=g), torch.randn(n, 128, generator=g)
+        fn = lambda: oracle.forward_backward(x, w, (None,) * 4, go)  # noqa: E731
+        sample = f"{n} rows, float32 autograd with stored activations (oracle/)"
+    fn()
+    t0, reps = time.perf_counter(), 0
+    while reps < 3 or (time.perf_counter() - t0 < 5 and reps < 50):
+        fn()
+        reps += 1
+    return n * reps / (time.perf_counter() - t0), threads, sample
+
+
 def run_reference(args, rank):
     if rank != 0:
         return
@@ -431,6 +472,9 @@ def main():
         rate, threads, _ = cpu_training_step_rate(steps=8, warmup=1, points=points)
         cpu_baseline = {"value": rate, "unit": "points/s", "cores": threads, "kind": "port",
                         "sample": f"8 steps of {points} points, float32 CPU port of the same step (oracle/)"}  # fmt: skip
+    elif rank == 0 and world == 1 and not args.no_cpu_baseline:
+        rate, threads, sample = cpu_operator_rate(args.workload)
+        cpu_baseline = {"value": rate, "unit": "points/s", "cores": threads, "kind": "port", "sample": sample}
 
     if rank == 0:
         line = {
