@@ -298,6 +298,57 @@ def test_backward_all_points_identical():
     assert nerr(t.grad, want) <= BWD_TOL_F32
 
 
+# ---- large batches: the coarsest dense levels are accumulated in shared memory -------------------
+
+
+@pytest.mark.parametrize(
+    "D,F,T,L,lo,hi,dtype",
+    [
+        (3, 2, 2**19, 16, 16, 2048, torch.float32),
+        (3, 4, 2**15, 8, 16, 512, torch.float32),
+        (2, 2, 2**19, 8, 16, 1024, torch.float32),  # 2-D: every level dense, several fit
+        (3, 1, 2**14, 4, 4, 64, torch.float32),
+        (3, 2, 2**19, 16, 16, 2048, torch.float16),
+        (3, 8, 2**14, 4, 16, 128, torch.bfloat16),
+        (3, 4, 2**21, 8, 16, 1024, torch.float32),  # 144 MB of levels: cut into cache-sized passes
+    ],
+)
+def test_large_batch_against_oracle(D, F, T, L, lo, hi, dtype):
+    N = 2**18 + 37
+    x, table, go, kw = make_case(N, D, F, T, L, lo, hi, dtype, seed=17)
+    want_out = oracle.encode(x, table, **kw)
+    want = oracle.encode_backward(x, go, table, **kw)
+    t = table.cuda().requires_grad_(True)
+    out = hash_encoding(x.cuda(), t, None, None, T, lo, hi, L)
+    if dtype == torch.float32:
+        assert nerr(out, want_out) <= FWD_TOL_F32
+    else:
+        torch.testing.assert_close(out.float().cpu(), want_out.float(), atol=1e-3, rtol=1e-2)
+    out.backward(go.cuda())
+    if dtype == torch.float32:
+        assert nerr(t.grad, want) <= BWD_TOL_F32
+    else:
+        torch.testing.assert_close(t.grad.float().cpu(), want.float(), atol=1e-3 * N, rtol=1e-2)
+        assert nerr(t.grad, want) <= (2e-2 if dtype == torch.float16 else 1e-1)
+
+
+@pytest.mark.parametrize("divider", [1, 2, 4])
+def test_backward_large_batch_equals_the_sum_of_its_halves(divider):
+    # the halves are below the batch size at which shared-memory accumulation starts
+    N, D, F, T, L, lo, hi = 2**18, 3, 2, 2**17, 8, 16, 512
+    x, table, go, _ = make_case(N, D, F, T, L, lo, hi, torch.float32, seed=19)
+    x, go = x.cuda(), go.cuda()
+
+    def grad(xs, gs):
+        t = table.cuda().requires_grad_(True)
+        hash_encoding(xs, t, None, None, T, lo, hi, L, divider, divider).backward(gs)
+        return t.grad
+
+    whole = grad(x, go)
+    halves = grad(x[: N // 2], go[: N // 2]) + grad(x[N // 2 :], go[N // 2 :])
+    assert nerr(whole, halves) <= BWD_TOL_F32
+
+
 # ---- size-independent properties at full benchmark sizes ---------------------------------------
 
 
