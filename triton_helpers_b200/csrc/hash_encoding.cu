@@ -564,22 +564,88 @@ hash_bwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, const
 constexpr int kCoarseThreads = 1024;
 constexpr int kCoarseSmemBytes = 200 * 1024;
 
-template <typename T, int F>
-__device__ __forceinline__ void smem_add_row(T *row, const float (&v)[F]) {
+// Shared-memory floating-point adds are compare-and-swap loops and the unit retires about one of
+// them per clock per SM, so a row is updated with as few as possible: one 16-byte or 8-byte
+// compare-and-swap covers a whole row where the row has that size.
+
+template <typename T, int N>
+__device__ __forceinline__ void add_packed(const void *old_bits, const float *v, void *new_bits) {
+    // old_bits/new_bits: N elements of T; v: N floats to add
     if constexpr (sizeof(T) == 4) {
 #pragma unroll
-        for (int f = 0; f < F; ++f) atomicAdd(reinterpret_cast<float *>(row) + f, v[f]);
+        for (int k = 0; k < N; ++k) static_cast<float *>(new_bits)[k] = static_cast<const float *>(old_bits)[k] + v[k];
+    } else {
+        using T2 = typename std::conditional<std::is_same<T, __half>::value, __half2, __nv_bfloat162>::type;
+#pragma unroll
+        for (int k = 0; k < N; k += 2) {
+            T2 add;
+            add.x = from_float<T>(v[k]);
+            add.y = from_float<T>(v[k + 1]);
+            static_cast<T2 *>(new_bits)[k / 2] = __hadd2(static_cast<const T2 *>(old_bits)[k / 2], add);
+        }
+    }
+}
+
+__device__ __forceinline__ ulonglong2 smem_cas128(void *addr, ulonglong2 expect, ulonglong2 desired) {
+    ulonglong2 old;
+    const unsigned a = static_cast<unsigned>(__cvta_generic_to_shared(addr));
+    asm volatile(
+        "{\n\t.reg .b128 e, d, o;\n\t"
+        "mov.b128 e, {%2, %3};\n\t"
+        "mov.b128 d, {%4, %5};\n\t"
+        "atom.relaxed.cta.shared.cas.b128 o, [%6], e, d;\n\t"
+        "mov.b128 {%0, %1}, o;\n\t}"
+        : "=l"(old.x), "=l"(old.y)
+        : "l"(expect.x), "l"(expect.y), "l"(desired.x), "l"(desired.y), "r"(a)
+        : "memory");
+    return old;
+}
+
+// 16 bytes of a row: N = 16 / sizeof(T) elements
+template <typename T>
+__device__ __forceinline__ void smem_add16(T *p, const float *v) {
+    constexpr int N = 16 / sizeof(T);
+    ulonglong2 seen = *reinterpret_cast<const ulonglong2 *>(p);
+    for (int tries = 0; tries < (1 << 20); ++tries) {  // bounded: contention ends when the other lanes finish
+        ulonglong2 next;
+        add_packed<T, N>(&seen, v, &next);
+        const ulonglong2 old = smem_cas128(p, seen, next);
+        if (old.x == seen.x && old.y == seen.y) break;
+        seen = old;
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ void smem_add8(T *p, const float *v) {
+    constexpr int N = 8 / sizeof(T);
+    unsigned long long seen = *reinterpret_cast<const unsigned long long *>(p);
+    for (int tries = 0; tries < (1 << 20); ++tries) {
+        unsigned long long next;
+        add_packed<T, N>(&seen, v, &next);
+        const unsigned long long old = atomicCAS(reinterpret_cast<unsigned long long *>(p), seen, next);
+        if (old == seen) break;
+        seen = old;
+    }
+}
+
+template <typename T, int F>
+__device__ __forceinline__ void smem_add_row(T *row, const float (&v)[F]) {
+    constexpr int kRowBytes = F * sizeof(T);
+    if constexpr (kRowBytes % 16 == 0) {
+#pragma unroll
+        for (int b = 0; b < kRowBytes / 16; ++b) smem_add16<T>(row + b * (16 / sizeof(T)), v + b * (16 / sizeof(T)));
+    } else if constexpr (kRowBytes == 8) {
+        smem_add8<T>(row, v);
+    } else if constexpr (sizeof(T) == 4) {
+        atomicAdd(reinterpret_cast<float *>(row), v[0]);
     } else if constexpr (F == 1) {
         atomicAdd(row, from_float<T>(v[0]));
     } else {
         using T2 = typename std::conditional<std::is_same<T, __half>::value, __half2, __nv_bfloat162>::type;
-#pragma unroll
-        for (int f = 0; f < F; f += 2) {
-            T2 pair;
-            pair.x = from_float<T>(v[f]);
-            pair.y = from_float<T>(v[f + 1]);
-            atomicAdd(reinterpret_cast<T2 *>(row + f), pair);
-        }
+        T2 pair;
+        pair.x = from_float<T>(v[0]);
+        pair.y = from_float<T>(v[1]);
+        atomicAdd(reinterpret_cast<T2 *>(row), pair);
     }
 }
 
@@ -623,8 +689,8 @@ hash_bwd_coarse_kernel(const __grid_constant__ LevelParams P, const CoordView cv
             for (int f = 0; f < F; ++f) go[f] = live ? to_float<T>(grad_out[i * go_stride + level * F + f]) : 0.f;
             T *base = acc + (P.offset[level] - first_row) * F;
 
-            // Shared-memory floating-point adds are compare-and-swap loops, so lanes that meet in one
-            // cell (clustered inputs) are summed in registers first and one of them does the add.
+            // lanes that meet in one cell (clustered inputs) are summed in registers first and one of
+            // them does the shared-memory add
             unsigned long long key = 0;
 #pragma unroll
             for (int d = 0; d < D; ++d) key = (key << 20) | (cell[d] & 0xfffffu);  // dense levels: res < 2^20
