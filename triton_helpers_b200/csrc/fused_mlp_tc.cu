@@ -59,9 +59,9 @@ struct TcPlan {
     int tmem_cols;      // power of two >= 32
 };
 
-__host__ __device__ inline TcPlan tc_plan(const MlpShape &s, bool backward) {
+__host__ __device__ inline TcPlan tc_plan(const MlpShape &s, bool backward, int forward_tiles = 2) {
     TcPlan p{};
-    p.act_tiles = backward ? s.depth + 1 : 2;  // forward: two tiles, alternating, so the next input can stream in
+    p.act_tiles = backward ? s.depth + 1 : forward_tiles;  // forward: two tiles per row tile in flight, alternating, so the next input can stream in
     p.dz_tiles = backward ? 2 : 0;
     int off = (p.act_tiles + p.dz_tiles) * kTileBytes;
     p.w_offset[0] = off;
@@ -286,6 +286,228 @@ mlp_fwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
     }
     TH_TRACE_END;
     cta_teardown(tmem, P.tmem_cols);
+}
+
+// ---- forward, several row tiles per CTA ------------------------------------------------------------
+//
+// The kernel above keeps one row tile per CTA in flight and every thread walks the same chain
+// (issue, wait, epilogue, barrier); only co-resident CTAs overlap, and each of them needs its own
+// copy of the weights.  Here one CTA per SM runs S independent "slots" of 128 threads (4 warps).
+// A slot is what a CTA is above - it owns 64 TMEM columns, two operand tiles and two mbarriers, and
+// walks its row tiles layer by layer - but the slots share the weights, and they never meet at a
+// CTA-wide barrier after set-up, so one slot's MMAs run under the other slots' epilogues:
+//
+//   warp 0 of the slot  : fetches the slot's next input tile by TMA (a box of 64 columns x 128 rows
+//                         lands in the operand-tile layout; rows past the end and columns past
+//                         d_in arrive as zeros), waits for the current one, issues each layer's
+//                         GEMM, commits it to `acc_full` and polls that barrier;
+//   all 4 warps         : meet at the slot's named barrier (the three other warps park there while
+//                         the MMAs run), turn their accumulator rows (thread = tile row =
+//                         TMEM lane) into the next layer's operand rows in place, or into output
+//                         rows in global memory, and meet at the slot's named barrier.
+//
+// Tile k of a slot computes in buffer k & 1 while the prefetch of tile k + 1 lands in the other.
+// Every mbarrier wait is bounded and watches a shared abort flag; after an abort a slot keeps the
+// SAME sequence of named barriers (doing no work) so nobody is left waiting at one.
+
+constexpr int kMaxSlots = 6;
+
+struct SlotBarriers {
+    unsigned long long in_full[kMaxSlots][2];
+    unsigned long long acc_full[kMaxSlots];
+};
+
+__device__ __forceinline__ bool pipe_wait(uint32_t bar, uint32_t parity, int *abort_flag) {
+    if (*reinterpret_cast<volatile int *>(abort_flag)) return false;
+    for (int poll = 0; poll < kWaitPolls; ++poll) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if ((poll & 63) == 63 && *reinterpret_cast<volatile int *>(abort_flag)) return false;
+    }
+    *reinterpret_cast<volatile int *>(abort_flag) = 1;
+    g_tc_status = 1;
+    return false;
+}
+
+__device__ __forceinline__ void slot_barrier(int slot) {
+    asm volatile("bar.sync %0, 128;" ::"r"(slot + 1) : "memory");
+}
+
+// One accumulator row (out_pad = 16, 32 or 64 columns) -> bias, activation, rounding -> 16-byte
+// chunks, each handed to `sink(chunk index, packed values)`; 32 columns per TMEM load.
+template <typename T, int ACT, bool BIAS, typename Sink>
+__device__ __forceinline__ void drain_row(uint32_t taddr, int out_pad, const float *bias, Sink sink) {
+    uint32_t raw[32];
+    if (out_pad == 16) {
+        tmem_ld16(taddr, raw);
+        tmem_ld_wait();
+#pragma unroll
+        for (int u = 0; u < 2; ++u) sink(u, finish8<T, ACT, BIAS>(raw + 8 * u, bias + 8 * u));
+        return;
+    }
+    for (int first = 0; first < out_pad; first += 32) {
+        tmem_ld32(taddr + first, raw);
+        tmem_ld_wait();
+#pragma unroll
+        for (int u = 0; u < 4; ++u) sink(first / 8 + u, finish8<T, ACT, BIAS>(raw + 8 * u, bias + first + 8 * u));
+    }
+}
+
+template <typename T, int ACT, bool BIAS, int S>
+__global__ void __launch_bounds__(128 * S, 1)
+mlp_fwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ WeightMaps maps,
+                    const __grid_constant__ CUtensorMap x_map, T *__restrict__ y, long long y_stride, long long n_rows,
+                    int y_vec) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint32_t tmem_holder;
+    __shared__ int abort_flag;
+    __shared__ __align__(8) unsigned long long wbar;
+    __shared__ __align__(8) SlotBarriers bars;
+    const TcPlan P = tc_plan(s, false, 2 * S);
+    constexpr int bf16 = std::is_same<T, __half>::value ? 0 : 1;
+    constexpr uint32_t kTmemCols = S * kAccCols <= 256 ? 256 : 512;
+    const int warp = threadIdx.x >> 5;
+
+    // ---- set-up: barriers, biases, weights, TMEM ----
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int i = 0; i < S; ++i) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars.in_full[i][0])), "r"(1u) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars.in_full[i][1])), "r"(1u) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars.acc_full[i])), "r"(1u) : "memory");
+        }
+    }
+    {
+        float *bias = reinterpret_cast<float *>(smem + P.bias_offset);
+        for (int e = threadIdx.x; e < (s.depth + 1) * kMaxDim; e += blockDim.x) {
+            const int layer = e / kMaxDim, c = e % kMaxDim;
+            float v = 0.f;
+            if (BIAS) {
+                if (layer == 0) {
+                    if (c < s.d_hid) v = to_float<T>(static_cast<const T *>(p.b_in)[c]);
+                } else if (layer < s.depth) {
+                    if (c < s.d_hid) v = to_float<T>(static_cast<const T *>(p.b_hid)[(layer - 1) * s.d_hid + c]);
+                } else if (c < s.d_out) {
+                    v = to_float<T>(static_cast<const T *>(p.b_out)[c]);
+                }
+            }
+            bias[e] = v;
+        }
+    }
+    const bool weights_ok = tma_stage_weights(smem, P, s, maps, &wbar);  // contains the barrier that publishes the inits
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_holder)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (!weights_ok) {
+        abort_flag = 1;
+        g_tc_status = 1;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_holder;
+    const float *bias = reinterpret_cast<const float *>(smem + P.bias_offset);
+
+    const long long n_tiles = (n_rows + kTileRows - 1) / kTileRows;
+    const long long first_tile = blockIdx.x;
+    const long long n_mine = first_tile < n_tiles ? (n_tiles - first_tile + gridDim.x - 1) / gridDim.x : 0;
+
+    // ---- the slot's life; nothing below depends on other slots ----
+    const int slot = warp >> 2;
+    const bool issuer = (warp & 3) == 0;
+    const int row = 32 * (warp & 3) + (threadIdx.x & 31);
+    const uint32_t acc = tmem + slot * kAccCols;
+    const uint32_t taddr = acc + (static_cast<uint32_t>(32 * (warp & 3)) << 16);
+    const uint32_t acc_bar = smem_addr(&bars.acc_full[slot]);
+    unsigned char *buffers = smem + 2 * slot * kTileBytes;
+    uint32_t acc_phase = 0;  // tracked by the issuer warp
+    TH_TRACE_BEGIN
+
+    auto fetch_input = [&](int b, long long k) {  // by the issuer warp
+        if (elect_one()) {
+            const uint32_t bar = smem_addr(&bars.in_full[slot][b]);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(static_cast<uint32_t>(kTileBytes))
+                         : "memory");
+            tma_load_2d(buffers + b * kTileBytes, &x_map, 0, static_cast<int>((first_tile + k * gridDim.x) * kTileRows), bar);
+        }
+        __syncwarp();
+    };
+    if (issuer && slot < n_mine && !abort_flag) fetch_input(0, slot);
+
+    for (long long k = slot, q = 0; k < n_mine; k += S, ++q) {
+        const int b = static_cast<int>(q & 1);
+        const long long row0 = (first_tile + k * gridDim.x) * kTileRows;
+        unsigned char *tile = buffers + b * kTileBytes;
+        const uint32_t tile_addr = smem_addr(tile);
+        const uint32_t row_addr = tile_addr + row * 128, row_swizzle = (row & 7) << 4;  // chunk c of the row: row_addr + ((c << 4) ^ row_swizzle)
+        if (issuer) {
+            TH_STAMP(40);
+            // the other buffer's last reader was the previous tile of this slot: finished
+            if (k + S < n_mine && !*reinterpret_cast<volatile int *>(&abort_flag)) fetch_input(b ^ 1, k + S);
+            TH_STAMP(41);
+            pipe_wait(smem_addr(&bars.in_full[slot][b]), static_cast<uint32_t>((q >> 1) & 1), &abort_flag);
+            TH_STAMP(42);
+        }
+        for (int l = 0; l <= s.depth; ++l) {
+            const int in_pad = l == 0 ? s.ki : s.h;
+            const int out_pad = l == s.depth ? s.no : s.h;
+            // Only the issuer warp polls the mbarrier; the slot's other warps park at the named barrier,
+            // which costs no issue slots.  A wait that gives up raises the abort flag, and everybody
+            // reads it after the barrier: work stops, the barrier sequence goes on.
+            if (issuer) {
+                if (__all_sync(0xffffffffu, !*reinterpret_cast<volatile int *>(&abort_flag))) {
+                    const bool leader = elect_one();
+                    tc_fence_after();
+                    issue_gemm(leader, acc, tile_addr, 32, smem_addr(weight_tile(smem, P, s, l)), 32, in_pad / 16,
+                               instr_desc(128, out_pad, bf16, 0, 0), false);
+                    if (leader) mma_commit(acc_bar);
+                    __syncwarp();
+                    TH_STAMP(43);
+                    pipe_wait(acc_bar, acc_phase, &abort_flag);
+                    acc_phase ^= 1u;
+                }
+                TH_STAMP(44);
+            }
+            slot_barrier(slot);
+            TH_STAMP(47);
+            if (!*reinterpret_cast<volatile int *>(&abort_flag)) {
+                tc_fence_after();
+                const float *layer_bias = bias + l * kMaxDim;
+                if (l < s.depth) {
+                    drain_row<T, ACT, BIAS>(taddr, out_pad, layer_bias, [&](int chunk, uint4 packed) {
+                        st_shared_16(row_addr + ((chunk << 4) ^ row_swizzle), packed);
+                    });
+                    fence_async_smem();
+                } else {
+                    const bool live = row0 + row < n_rows;
+                    T *out_row = y + (live ? row0 + row : 0) * y_stride;
+                    drain_row<T, TH_ACT_NONE, BIAS>(taddr, out_pad, layer_bias, [&](int chunk, uint4 packed) {
+                        if (live) store_chunk_to_global<T>(out_row, chunk, s.d_out, packed, y_vec);
+                    });
+                }
+                tc_fence_before();
+            }
+            TH_STAMP(45);
+            slot_barrier(slot);
+            TH_STAMP(46);
+        }
+    }
+
+    // ---- teardown ----
+    TH_TRACE_END;
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
 }
 
 // ---- backward ----------------------------------------------------------------------------------
@@ -536,11 +758,12 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 // One map per weight array: [rows][cols] 16-bit row-major, box = 64 columns x box_rows rows.
-bool make_map(CUtensorMap *map, const void *base, int rows, int cols, int box_rows) {
+bool make_map(CUtensorMap *map, const void *base, long long rows, int cols, int box_rows, long long row_stride = 0) {
     EncodeTiledFn encode = encode_tiled_fn();
-    if (!encode || !base || cols % 8 != 0 || !aligned_to(base, 16)) return false;
+    if (row_stride == 0) row_stride = cols;
+    if (!encode || !base || cols % 8 != 0 || row_stride % 8 != 0 || !aligned_to(base, 16)) return false;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_stride) * 2};
     const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
     const cuuint32_t elem[2] = {1, 1};
     return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void *>(base), dims, strides, box, elem,
@@ -574,9 +797,56 @@ bool tc_disabled() {
     return off;
 }
 
+// The pipelined kernel needs TMA for the weights and for the input rows, and enough shared memory
+// for two operand tiles per slot; anything else goes to the one-tile-per-CTA kernel below.
+bool pipe_disabled() {
+    static const bool off = [] {
+        const char *v = getenv("TH_MLP_NO_PIPE");
+        return v && v[0] == '1';
+    }();
+    return off;
+}
+
+template <typename T, int ACT, bool BIAS, int S>
+int launch_fwd_pipe(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, void *y, int64_t y_stride,
+                    int64_t rows, cudaStream_t stream) {
+    const TcPlan P = tc_plan(s, false, 2 * S);
+    const int smem = P.total + 1024;
+    if (smem > kSmemBudget || pipe_disabled()) return kTcNotApplicable;
+    if (rows >= (1ll << 31) - kTileRows) return kTcNotApplicable;  // TMA coordinates are 32-bit
+    WeightMaps maps;
+    CUtensorMap x_map;
+    if (!make_weight_maps(maps, s, p)) return kTcNotApplicable;
+    if (!make_map(&x_map, x, rows, s.d_in, kTileRows, x_stride)) return kTcNotApplicable;
+    auto kernel = mlp_fwd_pipe_kernel<T, ACT, BIAS, S>;
+    if (int rc = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+                             "cudaFuncSetAttribute(mlp_fwd_pipe_kernel)")) return rc;
+    const long long tiles = (rows + kTileRows - 1) / kTileRows;
+    const long long cap = sm_count();
+    kernel<<<static_cast<unsigned>(tiles < cap ? tiles : cap), 128 * S, smem, stream>>>(
+        s, p, maps, x_map, static_cast<T *>(y), y_stride, rows, rows_vector_ok(y, y_stride, s.d_out));
+    return cuda_status(cudaGetLastError(), "mlp_fwd_pipe_kernel launch");
+}
+
 template <typename T, int ACT, bool BIAS>
 int launch_fwd_t(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, void *y, int64_t y_stride,
                  int64_t rows, cudaStream_t stream) {
+    {
+        // Four slots measured best (2^21 rows, 32-64-64-16: 3 slots 0.136 ms, 4: 0.103, 5: 0.116, 6: 0.126;
+        // the kernel above: 0.193): MMA operand reads and epilogue stores share the SM's shared-memory
+        // bandwidth, and beyond four tiles in flight they only queue up behind each other.  Fewer are
+        // used when the weights leave less room; TH_MLP_SLOTS overrides the cap (0 = never).
+        static const int cap = [] {
+            const char *v = getenv("TH_MLP_SLOTS");
+            return v ? atoi(v) : 4;
+        }();
+        int rc = kTcNotApplicable;
+        if (cap >= 6) rc = launch_fwd_pipe<T, ACT, BIAS, 6>(s, p, x, x_stride, y, y_stride, rows, stream);
+        if (rc == kTcNotApplicable && cap >= 5) rc = launch_fwd_pipe<T, ACT, BIAS, 5>(s, p, x, x_stride, y, y_stride, rows, stream);
+        if (rc == kTcNotApplicable && cap >= 4) rc = launch_fwd_pipe<T, ACT, BIAS, 4>(s, p, x, x_stride, y, y_stride, rows, stream);
+        if (rc == kTcNotApplicable && cap >= 3) rc = launch_fwd_pipe<T, ACT, BIAS, 3>(s, p, x, x_stride, y, y_stride, rows, stream);
+        if (rc != kTcNotApplicable) return rc;
+    }
     const TcPlan P = tc_plan(s, false);
     int ctas = 0;
     const int smem = occupancy_plan(P, &ctas);

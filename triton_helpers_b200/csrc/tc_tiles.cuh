@@ -36,9 +36,12 @@ __device__ int g_tc_status = 0;  // 0 = fine, 1 = an mbarrier wait ran out
 __device__ long long g_trace[4096];
 __device__ int g_trace_n = 0;
 #define TH_TRACE_BEGIN int trace_i = 0;
+#ifndef TH_TRACE_THREAD
+#define TH_TRACE_THREAD 0
+#endif
 #define TH_STAMP(tag)                                                             \
     do {                                                                          \
-        if (blockIdx.x == 0 && threadIdx.x == 0 && trace_i < 2047) {              \
+        if (blockIdx.x == 0 && threadIdx.x == TH_TRACE_THREAD && trace_i < 2047) { \
             g_trace[2 * trace_i] = (tag);                                         \
             g_trace[2 * trace_i + 1] = clock64();                                 \
             ++trace_i;                                                            \
@@ -46,7 +49,7 @@ __device__ int g_trace_n = 0;
     } while (0)
 #define TH_TRACE_END                                                              \
     do {                                                                          \
-        if (blockIdx.x == 0 && threadIdx.x == 0) g_trace_n = trace_i;             \
+        if (blockIdx.x == 0 && threadIdx.x == TH_TRACE_THREAD) g_trace_n = trace_i; \
     } while (0)
 #else
 #define TH_TRACE_BEGIN
@@ -216,6 +219,75 @@ __device__ __forceinline__ uint4 finish_piece(const uint32_t (&raw)[8], const fl
         for (int k = 0; k < 4; ++k) w[k] = relu_pair<T>(w[k]);
     }
     return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// ---- lean epilogue pieces: 32 columns per TMEM load, fused convert + ReLU, 32-bit shared addresses ----
+
+// 32 consecutive accumulator columns of this thread's lane in one instruction
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+// two fp32 -> one packed 16-bit pair (lo in the low half), rounding to nearest even, with ReLU fused
+// into the conversion (negative results become +0; the same values as round-then-clamp)
+template <typename T>
+__device__ __forceinline__ uint32_t pack_pair_relu(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack_pair_relu<__half>(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+template <>
+__device__ __forceinline__ uint32_t pack_pair_relu<__nv_bfloat16>(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+
+__device__ __forceinline__ void st_shared_16(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// 8 fp32 accumulator columns (+ bias) -> activation -> one 16-byte chunk; the ReLU-without-bias case
+// is four instructions
+template <typename T, int ACT, bool BIAS>
+__device__ __forceinline__ uint4 finish8(const uint32_t *raw, const float *bias8) {
+    if constexpr (ACT == TH_ACT_RELU) {
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = __uint_as_float(raw[k]);
+        if constexpr (BIAS) {
+            const float4 b0 = *reinterpret_cast<const float4 *>(bias8), b1 = *reinterpret_cast<const float4 *>(bias8 + 4);
+            v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+            v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+        }
+        return make_uint4(pack_pair_relu<T>(v[0], v[1]), pack_pair_relu<T>(v[2], v[3]), pack_pair_relu<T>(v[4], v[5]),
+                          pack_pair_relu<T>(v[6], v[7]));
+    } else {
+        uint32_t r8[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) r8[k] = raw[k];
+        return finish_piece<T, ACT, BIAS>(r8, bias8);
+    }
 }
 
 // ---- operand tiles -----------------------------------------------------------------------------
