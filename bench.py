@@ -154,6 +154,7 @@ class TrainStep:
         self.targets = torch.rand(points, 16, device=device, generator=gen).half()
         self.table_elems = enc.embeddings.numel()
         self.units = points
+        self.gathers_per_step = points * 16 * 8  # one table row per corner per level
         self.host = None
 
     def step(self):
@@ -220,6 +221,7 @@ class HashOnly:
         self.table = ((torch.rand(geo.total_rows, c["feats"], device=device, generator=gen) * 2 - 1) * 1e-4).requires_grad_(True)
         self.go = torch.randn(c["points"], 16 * c["feats"], device=device, generator=gen)
         self.units = c["points"]
+        self.gathers_per_step = c["points"] * 16 * 8
 
     def step(self):
         c = self.c
@@ -399,6 +401,34 @@ def timed_region(fn, steps, world):
     return float(ms)
 
 
+def l2_probe(device):
+    r"""What the L2 delivers for the encoding's two access patterns, measured with ``th_probe_l2`` on a
+    24 MB buffer (the size of the cfg 3 float16 table): coalesced streaming reads in GB/s and
+    random 32-byte-sector gathers in 1e9 per second.  CUDA events on the launching stream."""
+    import ctypes
+
+    from triton_helpers_b200 import _lib
+
+    buf = torch.empty(24 * 2**20, dtype=torch.uint8, device=device).random_(0, 255)
+    sink = torch.zeros(1, dtype=torch.int32, device=device)
+    lib, stream = _lib.lib(), _lib.stream_ptr(device)
+    out = {}
+    for mode, iters, key, scale in ((0, 40, "stream_gbs", 1e9), (1, 64, "gather_g_per_s", 1e9)):
+        work = ctypes.c_int64(0)
+        call = lambda: _lib.check(lib.th_probe_l2(buf.data_ptr(), buf.numel(), mode, iters, sink.data_ptr(), ctypes.byref(work), stream), "th_probe_l2")  # noqa: E731
+        for _ in range(3):
+            call()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(5):
+            call()
+        stop.record()
+        torch.cuda.synchronize()
+        out[key] = work.value * 5 / (start.elapsed_time(stop) * 1e-3) / scale
+    out["buffer_mb"] = 24
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -466,6 +496,15 @@ def main():
                "h2d_bytes_per_step": wl.h2d_bytes, "d2h_bytes_per_step": wl.d2h_bytes,
                "last_loss": float(wl.loss_host[0])}  # fmt: skip
 
+    # the encoding kernels run out of L2 (cfg 0 / 3): put the cache's own figures beside the HBM roofline
+    l2 = None
+    if rank == 0 and args.workload in ("train_step", "hash", "contention"):
+        l2 = l2_probe(device)
+        fwd = kernels.get("th_hash_fwd")
+        if fwd and hasattr(wl, "gathers_per_step"):
+            l2["hash_fwd_gather_g_per_s"] = wl.gathers_per_step * args.steps / (fwd[1] * 1e-3) / 1e9
+            l2["hash_fwd_frac_of_gather_probe"] = l2["hash_fwd_gather_g_per_s"] / l2["gather_g_per_s"]
+
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload == "train_step":
         points = 2**17
@@ -485,7 +524,7 @@ def main():
                        "l2": "per-step inputs and intermediates exceed the 126 MB L2; no explicit flush"
                        if args.workload != "hash" else "table (48.8 MB) is meant to stay L2 resident; no flush"},
             "clocks": clock_summary, "e2e": e2e, "gpu_launches": wl.launches_per_step * args.steps,
-            "roofline": roofline, "kernels": breakdown, "cpu_baseline": cpu_baseline,
+            "roofline": roofline, "l2_probe": l2, "kernels": breakdown, "cpu_baseline": cpu_baseline,
         }  # fmt: skip
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -245,6 +245,16 @@ int th_adam_step(void *param_dev, void *grad_dev, float *exp_avg_dev, float *exp
                  float lr, float beta1, float beta2, float eps, int step, float grad_scale, int zero_grad,
                  int dtype, void *stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Measurement aid (no counterpart in triton_helpers): reads of an L2-resident buffer in the two
+ * patterns the hash encoding makes.  mode 0: coalesced 16-byte streaming reads, `iters` passes over
+ * the buffer; mode 1: 4-byte reads from pseudo-random 32-byte sectors, eight in flight per thread,
+ * `iters` rounds.  *work_out_host receives the bytes read (mode 0) or the number of gathers (mode 1)
+ * of the launch; the caller times it with CUDA events.  `sink_dev` is a 4-byte device scratch word.
+ * ------------------------------------------------------------------------------------------ */
+int th_probe_l2(const void *buffer_dev, int64_t n_bytes, int mode, int iters, void *sink_dev, int64_t *work_out_host,
+                void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -668,7 +668,9 @@ hash_bwd_coarse_kernel(const __grid_constant__ LevelParams P, const CoordView cv
     const long long end = begin + points_per_cta < n_points ? begin + points_per_cta : n_points;
     const unsigned lane = threadIdx.x & 31u;
     // whole warps stay in the loop so that the lanes can look for peers in the same cell
-    for (long long first = begin + (threadIdx.x & ~31u); first < end; first += kCoarseThreads) {
+    unsigned hot_levels = 0;  // warp-uniform: bit l set while level l keeps showing lanes in one cell
+    int batch = 0;
+    for (long long first = begin + (threadIdx.x & ~31u); first < end; first += kCoarseThreads, ++batch) {
         const long long i = first + lane;
         const bool live = i < end;
         float x[D];
@@ -691,12 +693,19 @@ hash_bwd_coarse_kernel(const __grid_constant__ LevelParams P, const CoordView cv
 
             // lanes that meet in one cell (clustered inputs) are summed in registers first and one of
             // them does the shared-memory add
-            unsigned long long key = 0;
+            // The search itself costs a match.any per level, so a warp only keeps it up on levels where
+            // the last search found something, and otherwise looks again every 8th batch of points.
+            unsigned peers = 1u << lane;
+            bool shared_cell = false;
+            if (((hot_levels >> level) & 1u) || (batch & 7) == 0) {
+                unsigned long long key = 0;
 #pragma unroll
-            for (int d = 0; d < D; ++d) key = (key << 20) | (cell[d] & 0xfffffu);  // dense levels: res < 2^20
-            if (!live) key = (1ull << 63) | lane;
-            const unsigned peers = __match_any_sync(0xffffffffu, key);
-            const bool shared_cell = __any_sync(0xffffffffu, (peers & (peers - 1)) != 0);
+                for (int d = 0; d < D; ++d) key = (key << 20) | (cell[d] & 0xfffffu);  // dense levels: res < 2^20
+                if (!live) key = (1ull << 63) | lane;
+                peers = __match_any_sync(0xffffffffu, key);
+                shared_cell = __any_sync(0xffffffffu, (peers & (peers - 1)) != 0);
+                hot_levels = shared_cell ? (hot_levels | (1u << level)) : (hot_levels & ~(1u << level));
+            }
             if (!shared_cell) {
                 if (live) {
 #pragma unroll

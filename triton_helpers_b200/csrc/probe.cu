@@ -1,0 +1,72 @@
+// Measurement aid: what this GPU's L2 delivers for the two access patterns the hash encoding makes,
+// so that the encoding kernels can be judged against the cache they actually run out of rather than
+// against HBM.  Not part of the operators; nothing here has a counterpart in triton_helpers.
+//
+//   mode 0  streaming reads : every thread walks the buffer in 16-byte steps, coalesced
+//   mode 1  sector gathers  : every thread reads 4 bytes from pseudo-random 32-byte sectors, eight
+//                             independent loads in flight (the eight corners of a grid cell)
+//
+// With a buffer of a few tens of MB and a warm-up pass the data comes from L2.  The caller times the
+// launch with CUDA events and divides: bytes = n_bytes * iters (mode 0), gathers = threads * 8 * iters
+// (mode 1, returned through *work_out).
+#include "common.cuh"
+
+namespace th {
+namespace {
+
+constexpr int kProbeThreads = 256;
+constexpr int kProbeCtasPerSm = 8;
+
+__global__ void __launch_bounds__(kProbeThreads) l2_stream_kernel(const uint4 *__restrict__ buf, long long n_vec, int iters,
+                                                                  unsigned *__restrict__ sink) {
+    unsigned acc = 0;
+    const long long stride = static_cast<long long>(gridDim.x) * kProbeThreads;
+    for (int it = 0; it < iters; ++it)
+        for (long long v = static_cast<long long>(blockIdx.x) * kProbeThreads + threadIdx.x; v < n_vec; v += stride) {
+            const uint4 q = __ldcg(buf + v);
+            acc ^= q.x ^ q.y ^ q.z ^ q.w;
+        }
+    if (acc == 0x9e3779b9u) *sink = acc;  // keeps the loads alive; practically never taken
+}
+
+__global__ void __launch_bounds__(kProbeThreads) l2_gather_kernel(const unsigned *__restrict__ buf, unsigned n_sectors, int iters,
+                                                                  unsigned *__restrict__ sink) {
+    unsigned state = (blockIdx.x * kProbeThreads + threadIdx.x) * 2654435761u + 12345u;
+    unsigned acc = 0;
+    for (int it = 0; it < iters; ++it) {
+        unsigned v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            state = state * 1664525u + 1013904223u;
+            const unsigned sector = static_cast<unsigned>((static_cast<unsigned long long>(state) * n_sectors) >> 32);
+            v[k] = __ldg(buf + static_cast<size_t>(sector) * 8 + (state & 7u));
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc ^= v[k];
+    }
+    if (acc == 0x9e3779b9u) *sink = acc;
+}
+
+}  // namespace
+}  // namespace th
+
+extern "C" int th_probe_l2(const void *buffer, int64_t n_bytes, int mode, int iters, void *sink, int64_t *work_out,
+                           void *stream) {
+    using namespace th;
+    if (!buffer || !sink || n_bytes < 4096 || iters < 1) return fail(TH_ERR_BAD_ARG, "th_probe_l2: buffer, sink, n_bytes >= 4096 and iters >= 1 are required");
+    if (!aligned_to(buffer, 16)) return fail(TH_ERR_ALIGNMENT, "th_probe_l2: buffer must be 16-byte aligned");
+    if (mode != 0 && mode != 1) return fail(TH_ERR_BAD_ARG, "th_probe_l2: mode is 0 (stream) or 1 (gather)");
+    const int ctas = sm_count() * kProbeCtasPerSm;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (mode == 0) {
+        const long long n_vec = n_bytes / 16;
+        l2_stream_kernel<<<ctas, kProbeThreads, 0, s>>>(static_cast<const uint4 *>(buffer), n_vec, iters, static_cast<unsigned *>(sink));
+        if (work_out) *work_out = n_vec * 16 * iters;
+    } else {
+        if (n_bytes / 32 > 0xffffffffll) return fail(TH_ERR_BAD_ARG, "th_probe_l2: buffer too large for the gather probe");
+        l2_gather_kernel<<<ctas, kProbeThreads, 0, s>>>(static_cast<const unsigned *>(buffer), static_cast<unsigned>(n_bytes / 32), iters,
+                                                        static_cast<unsigned *>(sink));
+        if (work_out) *work_out = static_cast<int64_t>(ctas) * kProbeThreads * 8 * iters;
+    }
+    return cuda_status(cudaGetLastError(), "th_probe_l2 launch");
+}
