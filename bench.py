@@ -11,6 +11,9 @@ targets copied in, the loss copied out, every step, inside the timed region).
 
 Other workloads (``hash`` = configuration 0, ``mlp`` = 1, ``reversible`` = 2, ``contention`` = 4)
 time forward + backward of one operator; with N > 1 every rank runs its own batch (no collective).
+On one GPU these are timed as CUDA-graph replays of one captured step (``--graph off`` for eager
+launches): their device work is shorter than the Python around it.  The per-kernel breakdown and
+the roofline always come from an eager pass with CUDA events around every C-ABI call.
 
 One JSON line is printed by rank 0.  ``--impl reference`` times the CPU port of the same step
 (``oracle/``: the restatement of the reference's torch CPU path) on the host cores instead.
@@ -201,7 +204,6 @@ class TrainStep:
             "th_adam_step": ("hbm", (3 * S + 16) * self.table_elems),
         }
 
-    launches_per_step = 1 + 1 + 1 + 2 + 1 + 4  # hash fwd, mlp fwd, mse, mlp bwd (+convert), hash bwd, adam x4
 
 
 class HashOnly:
@@ -233,7 +235,6 @@ class HashOnly:
         b = hash_bytes_per_point(16, self.c["feats"], 4) * self.units
         return {"th_hash_fwd": ("hbm", b), "th_hash_bwd": ("hbm", b)}
 
-    launches_per_step = 2
 
 
 class MlpOnly:
@@ -260,7 +261,6 @@ class MlpOnly:
         f = 2 * (32 * 64 + 3 * 64 * 64 + 64 * 16) * self.units
         return {"th_mlp_fwd": ("tensor", f), "th_mlp_bwd": ("tensor", 2 * f)}
 
-    launches_per_step = 3
 
 
 class ReversibleOnly:
@@ -287,7 +287,6 @@ class ReversibleOnly:
         f = 8 * 4 * 2 * 64 * 64 * self.units
         return {"th_rev_fwd": ("tensor", f), "th_rev_bwd": ("tensor", 2 * f)}
 
-    launches_per_step = 3
 
 
 def build_workload(name, device, rank):
@@ -437,6 +436,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="train_step", choices=["train_step", "hash", "mlp", "reversible", "contention"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
+                    help="time CUDA-graph replays of the step (auto: single-operator workloads on one GPU)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -458,13 +459,36 @@ def main():
     wl = build_workload(args.workload, device, rank)
     # the sampler starts before the warm-up (nvidia-smi takes ~100 ms to deliver its first line);
     # the busier half of its samples is what gets summarised
+    use_graph = args.graph == "on" or (args.graph == "auto" and world == 1 and args.workload != "train_step")
+    timing = "eager launches, CUDA events around the timed steps"
     with ClockSampler(local_rank) as clocks:
         for _ in range(args.warmup):
             wl.step()
         torch.cuda.synchronize()
+        launches_before = _lib.lib().th_launch_count()
         with _lib.KernelTimer() as timer:
             total_ms = timed_region(wl.step, args.steps, world)
         kernels = timer.summary()
+        launches = _lib.lib().th_launch_count() - launches_before
+        if use_graph:
+            # The single-operator steps are tens of microseconds of GPU work behind hundreds of
+            # microseconds of Python: replaying a captured step measures the kernels, the eager pass
+            # above keeps the per-kernel CUDA-event breakdown.
+            try:
+                side = torch.cuda.Stream(device=device)
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    wl.step()
+                torch.cuda.current_stream().wait_stream(side)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    wl.step()
+                for _ in range(args.warmup):
+                    graph.replay()
+                total_ms = timed_region(graph.replay, args.steps, world)
+                timing = "CUDA-graph replays of one captured step, CUDA events around the timed replays; per-kernel times from an eager pass"
+            except Exception as exc:  # noqa: BLE001  (report and keep the eager number)
+                timing += f" (graph capture failed: {type(exc).__name__}: {exc})"[:300]
     clock_summary = clocks.summary()
     ms_per_step = total_ms / args.steps
     value = wl.units * world / (ms_per_step * 1e-3)
@@ -522,8 +546,9 @@ def main():
             "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
             "config": {"workload": wl.name, "units_per_gpu_per_step": wl.units,
                        "l2": "per-step inputs and intermediates exceed the 126 MB L2; no explicit flush"
-                       if args.workload != "hash" else "table (48.8 MB) is meant to stay L2 resident; no flush"},
-            "clocks": clock_summary, "e2e": e2e, "gpu_launches": wl.launches_per_step * args.steps,
+                       if args.workload != "hash" else "table (48.8 MB) is meant to stay L2 resident; no flush",
+                       "timing": timing},
+            "clocks": clock_summary, "e2e": e2e, "gpu_launches": launches,
             "roofline": roofline, "l2_probe": l2, "kernels": breakdown, "cpu_baseline": cpu_baseline,
         }  # fmt: skip
         print(json.dumps(line), flush=True)

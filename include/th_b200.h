@@ -55,6 +55,10 @@ int th_version(void);
 /* Text for the last non-zero return value on this host thread ("" if none). */
 const char *th_last_error_string(void);
 
+/* Kernels launched by this library in this process so far, over all entry points and threads
+ * (no counterpart in triton_helpers; lets a harness state how many of its launches were these). */
+long long th_launch_count(void);
+
 /* ------------------------------------------------------------------------------------------
  * Multiresolution hash encoding
  *

@@ -79,6 +79,7 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_float, c_float, c_float, c_int, c_float, c_int,
          c_int, c_void_p],
     ),
+    "th_launch_count": (ctypes.c_longlong, []),
     "th_probe_l2": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, _I64P, c_void_p]),
 }  # fmt: skip
 

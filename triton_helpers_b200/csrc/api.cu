@@ -1,6 +1,7 @@
 // Library-wide entry points: version, error text, cached device attributes.
 #include "common.cuh"
 
+#include <atomic>
 #include <mutex>
 
 namespace th {
@@ -9,6 +10,10 @@ char *last_error_buffer() {
     static thread_local char buffer[kErrorBufferBytes] = "";
     return buffer;
 }
+
+static std::atomic<long long> g_launches{0};
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+long long launches_so_far() { return g_launches.load(std::memory_order_relaxed); }
 
 int sm_count() {
     static std::mutex guard;
@@ -27,5 +32,7 @@ int sm_count() {
 }  // namespace th
 
 extern "C" int th_version(void) { return 1; }
+
+extern "C" long long th_launch_count(void) { return th::launches_so_far(); }
 
 extern "C" const char *th_last_error_string(void) { return th::last_error_buffer(); }

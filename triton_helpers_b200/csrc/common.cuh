@@ -31,6 +31,13 @@ inline int cuda_status(cudaError_t err, const char *what) {
     return fail(static_cast<int>(err), "%s: %s", what, cudaGetErrorString(err));
 }
 
+// After every kernel launch: counts it (th_launch_count) and reports a launch error, if any.
+void note_launch();
+inline int launch_status(const char *what) {
+    note_launch();
+    return cuda_status(cudaGetLastError(), what);
+}
+
 // Number of SMs of the current device (cached per device).
 int sm_count();
 

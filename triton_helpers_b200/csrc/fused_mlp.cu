@@ -386,7 +386,7 @@ int launch_mlp_fwd(const MlpShape &s, const MlpParams &p, const void *x, int64_t
     mlp_fwd_kernel<T><<<grid, kThreadsMlp, L.total, stream>>>(s, p, static_cast<const T *>(x), x_stride,
                                                              static_cast<T *>(y), y_stride, rows,
                                                              pairs_ok(x, x_stride, s.d_in), pairs_ok(y, y_stride, s.d_out));
-    return cuda_status(cudaGetLastError(), "mlp_fwd_kernel launch");
+    return launch_status("mlp_fwd_kernel launch");
 }
 
 template <typename T>
@@ -408,12 +408,12 @@ int launch_mlp_bwd(const MlpShape &s, const MlpParams &p, const void *x, int64_t
             s, p, static_cast<const T *>(x), x_stride, static_cast<const T *>(go), go_stride, static_cast<T *>(gx),
             gx_stride, workspace, rows, pairs_ok(x, x_stride, s.d_in), pairs_ok(go, go_stride, s.d_out),
             gx ? pairs_ok(gx, gx_stride, s.d_in) : 0);
-        if (int rc = cuda_status(cudaGetLastError(), "mlp_bwd_kernel launch")) return rc;
+        if (int rc = launch_status("mlp_bwd_kernel launch")) return rc;
     }
     mlp_grad_convert_kernel<T><<<(W.total + 255) / 256, 256, 0, stream>>>(
         s, workspace, static_cast<T *>(dw_in), static_cast<T *>(dw_hid), static_cast<T *>(dw_out),
         static_cast<T *>(db_in), static_cast<T *>(db_hid), static_cast<T *>(db_out));
-    return cuda_status(cudaGetLastError(), "mlp_grad_convert_kernel launch");
+    return launch_status("mlp_grad_convert_kernel launch");
 }
 
 }  // namespace

@@ -825,7 +825,7 @@ int launch_fwd_pipe(const MlpShape &s, const MlpParams &p, const void *x, int64_
     const long long cap = sm_count();
     kernel<<<static_cast<unsigned>(tiles < cap ? tiles : cap), 128 * S, smem, stream>>>(
         s, p, maps, x_map, static_cast<T *>(y), y_stride, rows, rows_vector_ok(y, y_stride, s.d_out));
-    return cuda_status(cudaGetLastError(), "mlp_fwd_pipe_kernel launch");
+    return launch_status("mlp_fwd_pipe_kernel launch");
 }
 
 template <typename T, int ACT, bool BIAS>
@@ -861,7 +861,7 @@ int launch_fwd_t(const MlpShape &s, const MlpParams &p, const void *x, int64_t x
     kernel<<<static_cast<unsigned>(tiles < cap ? tiles : cap), kTcThreads, smem, stream>>>(
         s, p, maps, use_tma, static_cast<const T *>(x), x_stride, static_cast<T *>(y), y_stride, rows,
         rows_vector_ok(x, x_stride, s.d_in), rows_vector_ok(y, y_stride, s.d_out));
-    return cuda_status(cudaGetLastError(), "mlp_fwd_tc_kernel launch");
+    return launch_status("mlp_fwd_tc_kernel launch");
 }
 
 template <typename T, bool BIAS>
@@ -902,7 +902,7 @@ int launch_bwd_t(const MlpShape &s, const MlpParams &p, const void *x, int64_t x
         s, p, maps, use_tma, static_cast<const T *>(x), x_stride, static_cast<const T *>(go), go_stride, static_cast<T *>(gx), gx_stride,
         workspace, rows, rows_vector_ok(x, x_stride, s.d_in), rows_vector_ok(go, go_stride, s.d_out),
         gx ? rows_vector_ok(gx, gx_stride, s.d_in) : 0);
-    return cuda_status(cudaGetLastError(), "mlp_bwd_tc_kernel launch");
+    return launch_status("mlp_bwd_tc_kernel launch");
 }
 
 template <typename T>

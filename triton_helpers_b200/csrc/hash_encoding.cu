@@ -907,7 +907,7 @@ int launch_fwd(const LevelParams &P, const CoordView &cv, const void *table, voi
             case 2: hash_fwd_kernel<T, D, F, 2><<<grid, kThreads, 0, stream>>>(P, cv, tb, o, out_stride, n, a, b, vec); break;
             default: hash_fwd_kernel<T, D, F, 1><<<grid, kThreads, 0, stream>>>(P, cv, tb, o, out_stride, n, a, b, vec); break;
         }
-        if (int rc = cuda_status(cudaGetLastError(), "hash_fwd_kernel launch")) return rc;
+        if (int rc = launch_status("hash_fwd_kernel launch")) return rc;
     }
     return TH_OK;
 }
@@ -946,7 +946,7 @@ int launch_bwd(const LevelParams &P, const CoordView &cv, const void *go, int64_
         const int ctas = sm_count();
         const long long per_cta = (n + ctas - 1) / ctas;
         kernel<<<ctas, kCoarseThreads, bytes, stream>>>(P, cv, g, go_stride, gt, n, l0, coarse_end, per_cta);
-        if (int rc = cuda_status(cudaGetLastError(), "hash_bwd_coarse_kernel launch")) return rc;
+        if (int rc = launch_status("hash_bwd_coarse_kernel launch")) return rc;
         if (coarse_end == l1) return TH_OK;
     }
     // 2. everything else with global reductions, in passes that keep the rows being updated in L2
@@ -962,7 +962,7 @@ int launch_bwd(const LevelParams &P, const CoordView &cv, const void *go, int64_
             case 2: hash_bwd_kernel<T, D, F, 2><<<grid, kThreads, 0, stream>>>(P, cv, g, go_stride, gt, n, a, b, vec, coarse_end); break;
             default: hash_bwd_kernel<T, D, F, 1><<<grid, kThreads, 0, stream>>>(P, cv, g, go_stride, gt, n, a, b, vec, coarse_end); break;
         }
-        if (int rc = cuda_status(cudaGetLastError(), "hash_bwd_kernel launch")) return rc;
+        if (int rc = launch_status("hash_bwd_kernel launch")) return rc;
     }
     return TH_OK;
 }
@@ -1066,5 +1066,5 @@ extern "C" int th_hash_debug_indices(const void *coords_dev, int64_t coord_strid
         case 2: hash_debug_kernel<2><<<grid, kThreads, 0, s>>>(P, cv, io, weight_out_dev, n_points, n_levels); break;
         default: hash_debug_kernel<3><<<grid, kThreads, 0, s>>>(P, cv, io, weight_out_dev, n_points, n_levels); break;
     }
-    return cuda_status(cudaGetLastError(), "hash_debug_kernel launch");
+    return launch_status("hash_debug_kernel launch");
 }

@@ -150,7 +150,7 @@ extern "C" int th_mse_grad(const void *pred_dev, const void *target_dev, void *g
             break;
         default: return fail(TH_ERR_BAD_ARG, "unknown dtype %d", dtype);
     }
-    return cuda_status(cudaGetLastError(), "mse_grad_kernel launch");
+    return launch_status("mse_grad_kernel launch");
 }
 
 extern "C" int th_adam_step(void *param_dev, void *grad_dev, float *exp_avg_dev, float *exp_avg_sq_dev, int64_t n_elems,
@@ -179,5 +179,5 @@ extern "C" int th_adam_step(void *param_dev, void *grad_dev, float *exp_avg_dev,
             break;
         default: return fail(TH_ERR_BAD_ARG, "unknown dtype %d", dtype);
     }
-    return cuda_status(cudaGetLastError(), "adam_kernel launch");
+    return launch_status("adam_kernel launch");
 }

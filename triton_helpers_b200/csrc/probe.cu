@@ -68,5 +68,5 @@ extern "C" int th_probe_l2(const void *buffer, int64_t n_bytes, int mode, int it
                                                         static_cast<unsigned *>(sink));
         if (work_out) *work_out = static_cast<int64_t>(ctas) * kProbeThreads * 8 * iters;
     }
-    return cuda_status(cudaGetLastError(), "th_probe_l2 launch");
+    return launch_status("th_probe_l2 launch");
 }

@@ -417,7 +417,7 @@ int launch_rev_fwd(const RevShape &s, const RevParams &p, const void *x, int64_t
     const long long cap = static_cast<long long>(sm_count()) * 2;
     rev_fwd_kernel<T><<<static_cast<unsigned>(tiles < cap ? tiles : cap), kRevThreads, L.total, stream>>>(
         s, p, static_cast<const T *>(x), x_stride, static_cast<T *>(y), y_stride, rows);
-    return cuda_status(cudaGetLastError(), "rev_fwd_kernel launch");
+    return launch_status("rev_fwd_kernel launch");
 }
 
 template <typename T>
@@ -439,14 +439,14 @@ int launch_rev_bwd(const RevShape &s, const RevParams &p, const void *y, int64_t
         rev_bwd_kernel<T><<<grid, kRevThreads, L.total, stream>>>(
             s, p, static_cast<const T *>(y), y_stride, static_cast<const T *>(go), go_stride, static_cast<T *>(gx),
             gx_stride, static_cast<T *>(x_rec), xr_stride, workspace, rows);
-        if (int rc = cuda_status(cudaGetLastError(), "rev_bwd_kernel launch")) return rc;
+        if (int rc = launch_status("rev_bwd_kernel launch")) return rc;
     }
     const unsigned rgrid = static_cast<unsigned>((rev_cta_floats(s) + 255) / 256);
     rev_grad_reduce_kernel<T><<<rgrid, 256, 0, stream>>>(
         s, workspace, grid, static_cast<T *>(dw[0]), static_cast<T *>(dw[1]), static_cast<T *>(dw[2]),
         static_cast<T *>(dw[3]), static_cast<T *>(db[0]), static_cast<T *>(db[1]), static_cast<T *>(db[2]),
         static_cast<T *>(db[3]));
-    return cuda_status(cudaGetLastError(), "rev_grad_reduce_kernel launch");
+    return launch_status("rev_grad_reduce_kernel launch");
 }
 
 }  // namespace

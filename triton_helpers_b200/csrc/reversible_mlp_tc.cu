@@ -441,7 +441,7 @@ int launch_rev_fwd_t(const RevShape &s, const RevParams &p, const void *x, int64
     const long long cap = static_cast<long long>(sm_count()) * ctas;
     kernel<<<static_cast<unsigned>(tiles < cap ? tiles : cap), kTcThreads, smem, stream>>>(
         s, p, static_cast<const T *>(x), x_stride, static_cast<T *>(y), y_stride, rows);
-    return cuda_status(cudaGetLastError(), "rev_fwd_tc_kernel launch");
+    return launch_status("rev_fwd_tc_kernel launch");
 }
 
 template <typename T, bool BIAS>
@@ -474,12 +474,12 @@ int launch_rev_bwd_t(const RevShape &s, const RevParams &p, const void *y, int64
     kernel<<<n_ctas, kTcThreads, smem, stream>>>(s, p, static_cast<const T *>(y), y_stride, static_cast<const T *>(go),
                                                 go_stride, static_cast<T *>(gx), gx_stride, static_cast<T *>(x_rec),
                                                 xr_stride, workspace, rows);
-    if (int rc = cuda_status(cudaGetLastError(), "rev_bwd_tc_kernel launch")) return rc;
+    if (int rc = launch_status("rev_bwd_tc_kernel launch")) return rc;
     const size_t mat_total = static_cast<size_t>(s.blocks) * 4 * kMatFloats;
     rev_grad_reduce_tc_kernel<T><<<static_cast<unsigned>((mat_total + 255) / 256), 256, 0, stream>>>(
         s, workspace, n_ctas, static_cast<T *>(dw[0]), static_cast<T *>(dw[1]), static_cast<T *>(dw[2]),
         static_cast<T *>(dw[3]));
-    return cuda_status(cudaGetLastError(), "rev_grad_reduce_tc_kernel launch");
+    return launch_status("rev_grad_reduce_tc_kernel launch");
 }
 
 }  // namespace

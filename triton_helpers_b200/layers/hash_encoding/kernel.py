@@ -16,6 +16,7 @@ Differences a caller can observe:
   (:253-256) and so differs from its own CPU path in the last bit of some coordinates.
 """
 import math
+import weakref
 from typing import Final, Optional, Sequence, Tuple
 
 import torch
@@ -50,29 +51,63 @@ def _check_divider(divider: int, levels: int) -> None:
     assert divider & (divider - 1) == 0, "Divider must be a power of 2"
 
 
+_DEFAULT_PI: dict = {}
+
+
+def _default_pi(device: torch.device) -> Tensor:
+    r"""The built-in primes as an int64 tensor on ``device``, created once per device."""
+    pi = _DEFAULT_PI.get(device)
+    if pi is None:
+        pi = torch.tensor([PI_1, PI_2, PI_3], dtype=torch.int64, device=device)
+        _DEFAULT_PI[device] = pi
+    return pi
+
+
+_PRIMES_SEEN: dict = {}
+
+
+def host_primes(pi, D: int) -> Tuple[int, ...]:
+    r"""The first ``D`` hash primes as Python ints.  ``pi`` is a tensor (the module's buffer, usually
+    on the GPU) or an already extracted tuple.  Reading a device tensor synchronises the stream, which
+    would stall every forward and backward call behind the GPU, so the values are read once per tensor
+    object and version and remembered."""
+    if not isinstance(pi, Tensor):
+        return tuple(int(v) for v in pi[:D])
+    key = id(pi)
+    hit = _PRIMES_SEEN.get(key)
+    if hit is not None and hit[0]() is pi and hit[1] == pi._version and len(hit[2]) >= D:
+        return hit[2][:D]
+    values = tuple(int(v) for v in pi.tolist())
+    if len(_PRIMES_SEEN) > 256:
+        _PRIMES_SEEN.clear()
+    _PRIMES_SEEN[key] = (weakref.ref(pi, lambda _ref, key=key: _PRIMES_SEEN.pop(key, None)), pi._version, values)
+    return values[:D]
+
+
 class _Launch:
     r"""Host-side arguments shared by the forward, backward and debug entry points."""
 
-    def __init__(self, coords: Tensor, pi: Tensor, D: int, T: int, levels: int, min_res: int, max_res: int, scale: float):
+    def __init__(self, coords: Tensor, pi, D: int, T: int, levels: int, min_res: int, max_res: int, scale: float):
         geo = level_geometry(levels, T, D, min_res, max_res)
         self.geo = geo
         self._fill(coords, pi, D, geo.resolutions, geo.rows, geo.offsets, scale)
 
     @classmethod
-    def from_levels(cls, coords: Tensor, pi: Tensor, D: int, resolutions, rows, scale: float) -> "_Launch":
+    def from_levels(cls, coords: Tensor, pi, D: int, resolutions, rows, scale: float) -> "_Launch":
         self = cls.__new__(cls)
         self.geo = None
         offsets = [sum(rows[:i]) for i in range(len(rows))]
         self._fill(coords, pi, D, resolutions, rows, offsets, scale)
         return self
 
-    def _fill(self, coords: Tensor, pi: Tensor, D: int, resolutions, rows, offsets, scale: float) -> None:
+    def _fill(self, coords: Tensor, pi, D: int, resolutions, rows, offsets, scale: float) -> None:
         self.coords2d = _flatten_rows(coords, D)
         self.n = self.coords2d.shape[0]
         self.res = _lib.i32_array(list(resolutions))
         self.rows = _lib.i64_array(list(rows))
         self.offsets = _lib.i64_array(list(offsets))
-        self.primes = _lib.i64_array([int(v) for v in pi[:D].tolist()])
+        self.prime_values = host_primes(pi, D)
+        self.primes = _lib.i64_array(list(self.prime_values))
         self.scale = float(scale)
         self.coord_args = (
             self.coords2d.data_ptr(),
@@ -108,7 +143,7 @@ class HashEncoding(torch.autograd.Function):
         if pi is None:
             if D_in > 3:
                 raise ValueError("Pi must be provided for more than 3 dimensions")
-            pi = torch.tensor([PI_1, PI_2, PI_3], dtype=torch.int64, device=coords.device)
+            pi = _default_pi(coords.device)
         assert isinstance(pi, Tensor)
         assert pi.ndim == 1, "Pi must be a 1-dimensional tensor"
         assert pi.numel() >= D_in, "Pi must have at least D_in elements"
@@ -156,6 +191,7 @@ class HashEncoding(torch.autograd.Function):
             o[..., D_embed * levels :] = features
 
         ctx.save_for_backward(coords, embeddings, pi)
+        ctx.prime_values = launch.prime_values  # the backward pass needs no second look at `pi`
         ctx.max_entries_per_level = max_entries_per_level
         ctx.min_res = min_res
         ctx.max_res = max_res
@@ -175,7 +211,7 @@ class HashEncoding(torch.autograd.Function):
         if ctx.bwd_divider is not None:
             _check_divider(ctx.bwd_divider, levels)
 
-        launch = _Launch(coords, pi, D_in, ctx.max_entries_per_level, levels, ctx.min_res, ctx.max_res, ctx.scale)
+        launch = _Launch(coords, ctx.prime_values, D_in, ctx.max_entries_per_level, levels, ctx.min_res, ctx.max_res, ctx.scale)
         de = torch.zeros(embeddings.shape, dtype=embeddings.dtype, device=embeddings.device)
 
         D_out = do.shape[-1]
