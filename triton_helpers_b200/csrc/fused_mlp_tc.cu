@@ -317,9 +317,13 @@ struct SlotBarriers {
     unsigned long long acc_full[kMaxSlots];
 };
 
+// a poll that does not succeed comes back after a few microseconds: 2^16 of them are a fraction of a
+// second, orders of magnitude above any wait of a healthy run
+constexpr int kPipeWaitPolls = 1 << 16;
+
 __device__ __forceinline__ bool pipe_wait(uint32_t bar, uint32_t parity, int *abort_flag) {
     if (*reinterpret_cast<volatile int *>(abort_flag)) return false;
-    for (int poll = 0; poll < kWaitPolls; ++poll) {
+    for (int poll = 0; poll < kPipeWaitPolls; ++poll) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
@@ -603,6 +607,7 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
     uint32_t phase = 0;
     bool first_tile = true;
     const long long n_tiles = (n_rows + kTileRows - 1) / kTileRows;
+    TH_TRACE_BEGIN
     auto act_tile = [&](int l) { return smem + l * kTileBytes; };
     auto dw_col = [&](int l) { return kAccCols + (l == 0 ? 0 : s.ki + (l - 1) * s.h); };
 
@@ -617,6 +622,7 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
     }
     for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         const long long row0 = tile * kTileRows;
+        TH_STAMP(70);
         // ---- phase 1: recompute the forward, parking every layer input ----
         if (kPrefetch) {
             commit_tile(act_tile(0), x_next, s.ki);
@@ -630,6 +636,7 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
         fence_async_smem();
         tc_fence_before();
         __syncthreads();
+        TH_STAMP(71);
         if (abort_flag) break;
         if (kPrefetch && tile + gridDim.x < n_tiles) {
             fetch_tile<T>(x_next, x, x_stride, (tile + gridDim.x) * kTileRows, n_rows, s.d_in, s.ki, x_vec);
@@ -645,15 +652,19 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
                 if (leader) mma_commit(bar);
                 __syncwarp();
             }
+            TH_STAMP(72);
             const bool ok = cta_wait_mma(bar, phase, &abort_flag);
+            TH_STAMP(73);
             if (!ok) {
                 g_tc_status = 1;
             } else {
                 hidden_epilogue<T, ACT, false>(taddr, seat, s.h, nullptr, act_tile(l + 1));
             }
+            TH_STAMP(74);
             fence_async_smem();
             tc_fence_before();
             __syncthreads();
+            TH_STAMP(75);
             if (abort_flag) break;
         }
         if (abort_flag) break;
@@ -679,7 +690,9 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
                 if (leader) mma_commit(bar);
                 __syncwarp();
             }
+            TH_STAMP(76);
             const bool ok = cta_wait_mma(bar, phase, &abort_flag);
+            TH_STAMP(77);
             if (!ok) {
                 g_tc_status = 1;
             } else if (l > 0) {
@@ -689,9 +702,11 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
                 const bool live = row0 + seat.row < n_rows;
                 dx_epilogue<T>(taddr, seat, in_pad, gx + (live ? row0 + seat.row : 0) * gx_stride, s.d_in, live, gx_vec);
             }
+            TH_STAMP(78);
             fence_async_smem();
             tc_fence_before();
             __syncthreads();
+            TH_STAMP(79);
             if (abort_flag) break;
             buf ^= 1;
         }
@@ -699,6 +714,7 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
         first_tile = false;
     }
 
+    TH_TRACE_END;
     // ---- flush the weight gradients this CTA accumulated in TMEM ----
     if (!abort_flag && !first_tile) {
         tc_fence_after();
@@ -711,6 +727,284 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
         }
     }
     cta_teardown(tmem, P.tmem_cols);
+}
+
+// ---- backward, issuer warp + prefetched inputs ----------------------------------------------------
+//
+// Same dataflow as mlp_bwd_tc_kernel above (recompute and park, then dgrad + wgrad per layer with the
+// weight gradients resident in TMEM), reorganised so that less of it sits on the serial chain:
+//
+//   * warp 8 is the ISSUER.  It waits for an operand (mbarrier `ready`, 256 arrivals of the epilogue
+//     threads, or a TMA barrier), issues the layer's MMAs and commits: dgrad to `acc_full`, which the
+//     epilogue waits for, and wgrad after it to `wgrad_done`, which only the issuer itself waits for,
+//     one step later, before it reuses a buffer.  The 256 epilogue threads never issue or wait on wgrad.
+//   * the next row tile's x and grad_out tiles are fetched by TMA while the current tile is still in
+//     its last steps, into operand tiles the current tile has finished with: x into the buffer that
+//     held the input of the output layer (free once that layer's wgrad is done), grad_out into the dz
+//     buffer that held dz of layer 1 (free during the last step).  The activation buffers therefore
+//     rotate from tile to tile: layer l's input lives in buffer (base + l) mod (depth + 1).
+//   * epilogues read up to 32 accumulator columns per tcgen05.ld, convert with the ReLU fused into
+//     the rounding, and address shared memory with 32-bit shared addresses.
+//
+// Waiting for `acc_full`: warp 0 polls, the other seven epilogue warps park at named barrier 1 (256
+// threads).  All mbarrier waits are bounded and watch the abort flag; after an abort everybody keeps
+// the same barrier sequence without doing work.
+
+struct BwdBarriers {
+    // wgrad_done alternates between two barriers from step to step: the issuer waits for a step's
+    // wgrad one step late, after committing the next one, and a single barrier could then complete
+    // two phases between two looks at it, which a parity wait cannot tell from none.
+    unsigned long long in_x, in_go, acc_full, wgrad_done[2], ready;
+};
+
+template <typename T, int ACT>
+__global__ void __launch_bounds__(kTcThreads + 32, 2)
+mlp_bwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ WeightMaps maps,
+                    const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap go_map,
+                    T *__restrict__ gx, long long gx_stride, float *__restrict__ workspace, long long n_rows, int gx_vec) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint32_t tmem_holder;
+    __shared__ int abort_flag;
+    __shared__ __align__(8) unsigned long long wbar;
+    __shared__ __align__(8) BwdBarriers bars;
+    const TcPlan P = tc_plan(s, true);
+    constexpr int bf16 = std::is_same<T, __half>::value ? 0 : 1;
+    const int warp = threadIdx.x >> 5;
+    const int d = s.depth;  // layers 0 .. d; layer d is the output layer
+    const int n_act = d + 1;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars.in_x)), "r"(1u) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars.in_go)), "r"(1u) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars.acc_full)), "r"(1u) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars.wgrad_done[0])), "r"(1u) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars.wgrad_done[1])), "r"(1u) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars.ready)), "r"(static_cast<uint32_t>(kTcThreads)) : "memory");
+    }
+    // operand tiles start out as zeros: columns a layer does not use are still read as MMA rows
+    for (int e = threadIdx.x; e < (P.act_tiles + P.dz_tiles) * kTileBytes / 16; e += blockDim.x)
+        reinterpret_cast<uint4 *>(smem)[e] = make_uint4(0, 0, 0, 0);
+    fence_async_smem();
+    const bool weights_ok = tma_stage_weights(smem, P, s, maps, &wbar);  // contains the barrier that publishes the inits
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_holder)),
+                     "r"(static_cast<uint32_t>(P.tmem_cols))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (!weights_ok) {
+        abort_flag = 1;
+        g_tc_status = 1;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_holder;
+
+    const long long n_tiles = (n_rows + kTileRows - 1) / kTileRows;
+    const long long first_tile = blockIdx.x;
+    const long long n_mine = first_tile < n_tiles ? (n_tiles - first_tile + gridDim.x - 1) / gridDim.x : 0;
+    const uint32_t smem_base = smem_addr(smem);
+    const uint32_t dz_base = smem_base + P.act_tiles * kTileBytes;
+    auto dw_col = [&](int l) { return kAccCols + (l == 0 ? 0 : s.ki + (l - 1) * s.h); };
+    auto weight_addr = [&](int l) { return smem_addr(weight_tile(smem, P, s, l)); };
+    const uint32_t acc_bar = smem_addr(&bars.acc_full), ready_bar = smem_addr(&bars.ready);
+    volatile int *abort_now = &abort_flag;
+    TH_TRACE_BEGIN
+
+    if (warp == 8) {
+        // ================= issuer =================
+        const uint32_t x_bar = smem_addr(&bars.in_x), go_bar = smem_addr(&bars.in_go);
+        const uint32_t wg_bar[2] = {smem_addr(&bars.wgrad_done[0]), smem_addr(&bars.wgrad_done[1])};
+        uint32_t wg_phases = 0;  // bit b: parity of the next phase of wgrad_done[b] to wait for
+        unsigned step = 0;       // counts backward steps over all tiles; step j commits to wgrad_done[j & 1]
+        auto wait_wgrad = [&](unsigned j) {  // wgrad of step j has finished
+            const unsigned b = j & 1u;
+            const bool ok = __all_sync(0xffffffffu, pipe_wait(wg_bar[b], (wg_phases >> b) & 1u, &abort_flag));
+            wg_phases ^= 1u << b;
+            return ok;
+        };
+        auto fetch = [&](const CUtensorMap *map, uint32_t dst, uint32_t bar, long long k) {
+            if (elect_one()) {
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(static_cast<uint32_t>(kTileBytes)) : "memory");
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                    "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(static_cast<int>((first_tile + k * gridDim.x) * kTileRows)), "r"(bar)
+                    : "memory");
+            }
+            __syncwarp();
+        };
+        int base = 0, zs = 0;
+        uint32_t ready_phase = 0, in_phase = 0;
+        bool alive = !*abort_now;
+        if (alive && n_mine > 0) {
+            fetch(&x_map, smem_base, x_bar, 0);
+            fetch(&go_map, dz_base, go_bar, 0);
+        }
+        for (long long k = 0; alive && k < n_mine; ++k) {
+            auto act_addr = [&](int l) { return smem_base + static_cast<uint32_t>((base + l) % n_act) * kTileBytes; };
+            // ---- phase 1: recompute ----
+            for (int l = 0; alive && l < d; ++l) {
+                if (l > 0 || k > 0) {
+                    alive = pipe_wait(ready_bar, ready_phase, &abort_flag);
+                    ready_phase ^= 1u;
+                }
+                if (alive && l == 0) alive = pipe_wait(x_bar, in_phase, &abort_flag);
+                alive = __all_sync(0xffffffffu, alive);
+                if (!alive) break;
+                const bool leader = elect_one();
+                tc_fence_after();
+                issue_gemm(leader, tmem, act_addr(l), 32, weight_addr(l), 32, (l == 0 ? s.ki : s.h) / 16,
+                           instr_desc(128, s.h, bf16, 0, 0), false);
+                if (leader) mma_commit(acc_bar);
+                __syncwarp();
+            }
+            // ---- phase 2: layers backwards ----
+            for (int l = d; alive && l >= 0; --l) {
+                const int in_pad = l == 0 ? s.ki : s.h;
+                const int out_pad = l == d ? s.no : s.h;
+                const uint32_t dz = dz_base + static_cast<uint32_t>(zs ^ ((d - l) & 1)) * kTileBytes;
+                if (d > 0 || k > 0) {
+                    alive = pipe_wait(ready_bar, ready_phase, &abort_flag);
+                    ready_phase ^= 1u;
+                }
+                if (alive && d == 0) alive = pipe_wait(x_bar, in_phase, &abort_flag);  // no recompute phase: x is first used here
+                if (alive && l == d) alive = pipe_wait(go_bar, in_phase, &abort_flag);
+                alive = __all_sync(0xffffffffu, alive);
+                if (!alive) break;
+                const bool leader = elect_one();
+                tc_fence_after();
+                if (l > 0 || gx != nullptr)
+                    issue_gemm(leader, tmem, dz, 32, weight_addr(l), 2048, out_pad / 16, instr_desc(128, in_pad, bf16, 0, 1), false);
+                if (leader) mma_commit(acc_bar);
+                issue_gemm(leader, tmem + dw_col(l), dz, 2048, act_addr(l), 2048, kTileRows / 16, instr_desc(64, in_pad, bf16, 1, 1),
+                           k > 0);
+                if (leader) mma_commit(wg_bar[step & 1u]);
+                __syncwarp();
+                ++step;
+                // Buffers of step l + 1 are free once its wgrad is done (committed one step ago).
+                if (l < d) {
+                    alive = wait_wgrad(step - 2);
+                    if (!alive) break;
+                    if (k + 1 < n_mine) {
+                        if (l == d - 1) fetch(&x_map, act_addr(d), x_bar, k + 1);  // becomes the next tile's buffer 0
+                        if (l == 0) fetch(&go_map, dz_base + static_cast<uint32_t>(zs ^ ((d - 1) & 1)) * kTileBytes, go_bar, k + 1);
+                    }
+                }
+            }
+            if (!alive) break;
+            if (d == 0) {
+                // a single layer: nothing above freed its buffers early; wait for this tile's wgrad, then fetch
+                alive = wait_wgrad(step - 1);
+                if (alive && k + 1 < n_mine) {
+                    fetch(&x_map, smem_base, x_bar, k + 1);
+                    fetch(&go_map, dz_base + static_cast<uint32_t>(zs) * kTileBytes, go_bar, k + 1);
+                }
+            } else {
+                // the last step's wgrad: every commit is waited for exactly once, in order
+                alive = wait_wgrad(step - 1);
+                base = (base + d) % n_act;
+                zs ^= (d - 1) & 1;
+            }
+            in_phase ^= 1u;
+        }
+    } else {
+        // ================= epilogue threads =================
+        const Seat seat;
+        const uint32_t taddr = tmem + seat.lane_base;
+        const uint32_t row_off = seat.row * 128, row_swizzle = (seat.row & 7) << 4;
+        uint32_t acc_phase = 0;
+        int base = 0, zs = 0;
+        // wait for the accumulator: warp 0 polls, everybody meets at named barrier 1
+        auto wait_acc = [&]() {
+            if (warp == 0) {
+                pipe_wait(acc_bar, acc_phase, &abort_flag);
+                tc_fence_after();
+                tc_fence_before();
+            }
+            acc_phase ^= 1u;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            tc_fence_after();
+            return !*abort_now;
+        };
+        auto publish = [&]() {
+            fence_async_smem();
+            tc_fence_before();
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ready_bar) : "memory");
+        };
+        for (long long k = 0; k < n_mine; ++k) {
+            const long long row0 = (first_tile + k * gridDim.x) * kTileRows;
+            auto act_addr = [&](int l) { return smem_base + static_cast<uint32_t>((base + l) % n_act) * kTileBytes; };
+            // ---- phase 1 ----
+            for (int l = 0; l < d; ++l) {
+                if (wait_acc()) {
+                    const int n = s.h / kGroups;  // this thread's columns
+                    const uint32_t dst = act_addr(l + 1) + row_off;
+                    const int first = seat.group * (n / 8);
+                    for_each_piece(taddr + seat.group * n, n, [&](int u, const uint32_t(&piece)[8]) {
+                        st_shared_16(dst + (((first + u) << 4) ^ row_swizzle), finish8<T, ACT, false>(piece, nullptr));
+                    });
+                }
+                publish();
+            }
+            // ---- phase 2 ----
+            for (int l = d; l >= 0; --l) {
+                const int in_pad = l == 0 ? s.ki : s.h;
+                const bool ok = wait_acc();
+                const int n = in_pad / kGroups;
+                const int first = seat.group * (n / 8);
+                if (ok && l > 0) {
+                    const uint32_t parked = act_addr(l) + row_off;
+                    const uint32_t dst = dz_base + static_cast<uint32_t>(zs ^ ((d - l) & 1) ^ 1) * kTileBytes + row_off;
+                    for_each_piece(taddr + seat.group * n, n, [&](int u, const uint32_t(&piece)[8]) {
+                        const uint32_t off = ((first + u) << 4) ^ row_swizzle;
+                        uint4 g = finish8<T, TH_ACT_NONE, false>(piece, nullptr);
+                        if constexpr (ACT == TH_ACT_RELU) {
+                            const uint4 a = ld_shared_16(parked + off);
+                            g.x = keep_where_positive<T>(g.x, a.x);
+                            g.y = keep_where_positive<T>(g.y, a.y);
+                            g.z = keep_where_positive<T>(g.z, a.z);
+                            g.w = keep_where_positive<T>(g.w, a.w);
+                        }
+                        st_shared_16(dst + off, g);
+                    });
+                } else if (ok && gx != nullptr) {
+                    const bool live = row0 + seat.row < n_rows;
+                    T *row_ptr = gx + (live ? row0 + seat.row : 0) * gx_stride;
+                    for_each_piece(taddr + seat.group * n, n, [&](int u, const uint32_t(&piece)[8]) {
+                        if (live) store_chunk_to_global<T>(row_ptr, first + u, s.d_in, finish8<T, TH_ACT_NONE, false>(piece, nullptr), gx_vec);
+                    });
+                }
+                publish();
+            }
+            if (d > 0) {
+                base = (base + d) % n_act;
+                zs ^= (d - 1) & 1;
+            }
+        }
+    }
+    TH_TRACE_END;
+
+    // ---- flush the weight gradients this CTA accumulated in TMEM ----
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (!abort_flag && n_mine > 0 && warp < 8) {
+        const Seat seat;
+        const MlpGradWorkspace W = grad_workspace_layout(s, workspace);
+        for (int l = 0; l <= d; ++l) {
+            const int in_pad = l == 0 ? s.ki : s.h;
+            const int in_dim = l == 0 ? s.d_in : s.d_hid, out_dim = l == d ? s.d_out : s.d_hid;
+            float *dst = W.base + (l == 0 ? W.w_in : (l == d ? W.w_out : W.w_hid + (l - 1) * s.d_hid * s.d_hid));
+            flush_dw(tmem + seat.lane_base + dw_col(l), seat, in_pad, dst, out_dim, in_dim);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(static_cast<uint32_t>(P.tmem_cols)) : "memory");
 }
 
 // ---- host side ---------------------------------------------------------------------------------
@@ -883,8 +1177,41 @@ int launch_fwd(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_s
 }
 
 template <typename T, int ACT>
+int launch_bwd_pipe(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, const void *go, int64_t go_stride,
+                    void *gx, int64_t gx_stride, float *workspace, int64_t rows, cudaStream_t stream) {
+    if (pipe_disabled() || rows >= (1ll << 31) - kTileRows) return kTcNotApplicable;
+    const TcPlan P = tc_plan(s, true);
+    if (P.tmem_cols > 512) return kTcNotApplicable;
+    int ctas = 0;
+    const int smem = occupancy_plan(P, &ctas);
+    // With a single CTA per SM (deep networks: depth + 3 operand tiles) one row tile is in flight and the
+    // extra barrier round trips between issuer and epilogue cost more than the overlap gains (2^20 rows,
+    // 32-64x4-16: 0.534 ms against 0.494 ms for the kernel above); with two CTAs it is 0.378 against 0.470
+    // (2^21 rows, 32-64-64-16).
+    if (ctas < 2) return kTcNotApplicable;
+    if (ctas > 2) ctas = 2;  // the kernel is compiled for two CTAs of 288 threads per SM
+    WeightMaps maps;
+    CUtensorMap x_map, go_map;
+    if (!make_weight_maps(maps, s, p)) return kTcNotApplicable;
+    if (!make_map(&x_map, x, rows, s.d_in, kTileRows, x_stride)) return kTcNotApplicable;
+    if (!make_map(&go_map, go, rows, s.d_out, kTileRows, go_stride)) return kTcNotApplicable;
+    auto kernel = mlp_bwd_pipe_kernel<T, ACT>;
+    if (int rc = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+                             "cudaFuncSetAttribute(mlp_bwd_pipe_kernel)")) return rc;
+    const long long tiles = (rows + kTileRows - 1) / kTileRows;
+    const long long cap = static_cast<long long>(sm_count()) * ctas;
+    kernel<<<static_cast<unsigned>(tiles < cap ? tiles : cap), kTcThreads + 32, smem, stream>>>(
+        s, p, maps, x_map, go_map, static_cast<T *>(gx), gx_stride, workspace, rows, gx ? rows_vector_ok(gx, gx_stride, s.d_in) : 0);
+    return launch_status("mlp_bwd_pipe_kernel launch");
+}
+
+template <typename T, int ACT>
 int launch_bwd_t(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, const void *go, int64_t go_stride,
                  void *gx, int64_t gx_stride, float *workspace, int64_t rows, cudaStream_t stream) {
+    {
+        const int rc = launch_bwd_pipe<T, ACT>(s, p, x, x_stride, go, go_stride, gx, gx_stride, workspace, rows, stream);
+        if (rc != kTcNotApplicable) return rc;
+    }
     const TcPlan P = tc_plan(s, true);
     if (P.tmem_cols > 512) return kTcNotApplicable;
     int ctas = 0;

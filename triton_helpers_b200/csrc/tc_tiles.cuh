@@ -267,6 +267,43 @@ __device__ __forceinline__ void st_shared_16(uint32_t addr, uint4 v) {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+__device__ __forceinline__ uint4 ld_shared_16(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+
+// N (8, 16 or 32) consecutive accumulator columns of this thread's lane, then `fn(u, eight values)`
+// for each 8-column piece u; everything is sized at compile time so the values stay in registers.
+template <int N, typename Fn>
+__device__ __forceinline__ void for_each_piece_n(uint32_t taddr, Fn fn) {
+    uint32_t raw[32];
+    if constexpr (N == 32) {
+        tmem_ld32(taddr, raw);
+    } else if constexpr (N == 16) {
+        tmem_ld16(taddr, raw);
+    } else {
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                     : "=r"(raw[0]), "=r"(raw[1]), "=r"(raw[2]), "=r"(raw[3]), "=r"(raw[4]), "=r"(raw[5]), "=r"(raw[6]), "=r"(raw[7])
+                     : "r"(taddr)
+                     : "memory");
+    }
+    tmem_ld_wait();
+#pragma unroll
+    for (int u = 0; u < N / 8; ++u) {
+        const uint32_t piece[8] = {raw[8 * u], raw[8 * u + 1], raw[8 * u + 2], raw[8 * u + 3],
+                                   raw[8 * u + 4], raw[8 * u + 5], raw[8 * u + 6], raw[8 * u + 7]};
+        fn(u, piece);
+    }
+}
+// the same for a run-time n in {8, 16, 32} (warp uniform)
+template <typename Fn>
+__device__ __forceinline__ void for_each_piece(uint32_t taddr, int n, Fn fn) {
+    if (n == 32) for_each_piece_n<32>(taddr, fn);
+    else if (n == 16) for_each_piece_n<16>(taddr, fn);
+    else for_each_piece_n<8>(taddr, fn);
+}
+
 // 8 fp32 accumulator columns (+ bias) -> activation -> one 16-byte chunk; the ReLU-without-bias case
 // is four instructions
 template <typename T, int ACT, bool BIAS>
