@@ -145,6 +145,31 @@ def test_forward_backward_shapes_against_oracle(dtype, rows, d_in, d_hid, d_out,
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("depth,d_hid", [(1, 64), (2, 64), (3, 64), (2, 32), (3, 16)])
+def test_many_row_tiles_per_cta(dtype, depth, d_hid):
+    # Enough rows that every CTA of the tensor-core kernels walks several row tiles: the backward
+    # kernel prefetches the next tile into buffers the current one has finished with, and the roles of
+    # its operand tiles rotate from tile to tile (differently for odd and even depth).
+    rows = 148 * 2 * 128 * 3 + 77
+    p = make_params(32, d_hid, 16, depth, dtype, bias=False, seed=depth)
+    g = torch.Generator().manual_seed(depth)
+    x = torch.randn(1, rows, 32, generator=g).to(dtype)
+    go = torch.randn(1, rows, 16, generator=g).mul(1e-1).to(dtype).float()
+    want, got = run_both(x, p, go, "relu", rounded=True)
+    tight = 2e-3 if dtype == torch.float16 else 1.6e-2
+    for name, w, gg in zip(NAMES, want, got):
+        assert (w is None) == (gg is None), name
+        if w is None:
+            continue
+        if name == "dx":
+            assert rows_outside(gg, w, tight) <= 1e-2, f"dx rows outside: {rows_outside(gg, w, tight)}"
+            assert nerr(gg, w) <= 0.5
+        else:
+            # weight gradients are sums over 113 741 rows of 16-bit-rounded products
+            assert nerr(gg, w) <= (tight if name == "y" else 10 * tight), f"{name}: {nerr(gg, w)}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_baseline_configuration_full_size(dtype):
     # 2^20 rows, 32 -> 4 hidden layers of 64 (ReLU) -> 16, no bias, grad_out ~ 1e-2 N(0, 1)
     rows = 2**20

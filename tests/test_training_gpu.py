@@ -4,6 +4,7 @@ import pytest
 import torch
 
 from oracle.training_step import CpuNeuralField, make_batch
+from triton_helpers_b200 import _lib
 from triton_helpers_b200.layers.fully_fused_mlp import FullyFusedMLP
 from triton_helpers_b200.layers.hash_encoding import HashEncoding
 from triton_helpers_b200.optim import FusedAdam
@@ -90,3 +91,42 @@ def test_training_step_tracks_the_cpu_port():
         got = trainer(coords.cuda())
         want = fresh.predict(coords)
     assert float((got.float().cpu() - want).abs().max() / want.abs().max()) <= 1e-2
+
+
+# ---- measurement entry points ---------------------------------------------------------------------
+
+
+def test_launch_counter_and_l2_probe():
+    import ctypes
+
+    lib = _lib.lib()
+    device = torch.device("cuda", 0)
+    buf = torch.zeros(8 * 2**20, dtype=torch.uint8, device=device)
+    sink = torch.zeros(1, dtype=torch.int32, device=device)
+    before = lib.th_launch_count()
+    for mode, expect in ((0, 8 * 2**20 * 3), (1, None)):
+        work = ctypes.c_int64(0)
+        _lib.check(lib.th_probe_l2(buf.data_ptr(), buf.numel(), mode, 3, sink.data_ptr(), ctypes.byref(work), _lib.stream_ptr(device)), "th_probe_l2")
+        assert work.value > 0 and (expect is None or work.value == expect)
+    torch.cuda.synchronize()
+    assert lib.th_launch_count() - before == 2
+    # argument errors are reported, not launched
+    assert lib.th_probe_l2(buf.data_ptr(), buf.numel(), 7, 1, sink.data_ptr(), None, _lib.stream_ptr(device)) < 0
+    assert lib.th_launch_count() - before == 2
+
+
+def test_no_stream_synchronisation_in_the_encoding_calls():
+    # Forward and backward only enqueue work: the hash primes are read from the device once per
+    # tensor, not on every call (a read would serialise the host behind the GPU).
+    from triton_helpers_b200.layers.hash_encoding import HashEncoding
+
+    enc = HashEncoding(2**14, 8, 3, 2, 16, 256).cuda()
+    x = torch.rand(4096, 3, device="cuda")
+    enc(x).sum().backward()  # first call may read `pi`
+    torch.cuda.synchronize()
+    torch.cuda.set_sync_debug_mode("error")
+    try:
+        out = enc(x)
+        out.backward(torch.ones_like(out))
+    finally:
+        torch.cuda.set_sync_debug_mode("default")
