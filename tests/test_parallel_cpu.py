@@ -9,7 +9,14 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from triton_helpers_b200.parallel import allreduce_gradients, init_from_env, plan_buckets, shard_bounds
+from triton_helpers_b200.parallel import (
+    PendingReduce,
+    allreduce_gradients,
+    init_from_env,
+    level_passes,
+    plan_buckets,
+    shard_bounds,
+)
 
 
 def test_shard_bounds_cover_everything_once():
@@ -26,6 +33,27 @@ def test_plan_buckets():
     assert plan_buckets([10, 2000, 30], 100) == [[1], [0, 2]]
     assert plan_buckets([60, 60, 60], 100) == [[0], [1], [2]]
     assert plan_buckets([], 100) == []
+
+
+def test_level_passes_cover_every_level_once_finest_first():
+    from triton_helpers_b200.layers.hash_encoding.helpers import level_geometry
+
+    for rows in (level_geometry(16, 2**19, 3, 16, 2048).rows, level_geometry(16, 2**22, 3, 16, 4096).rows, [7] * 8, [3, 3]):
+        for n in (1, 2, 3, 4, 9):
+            passes = level_passes(rows, n)
+            assert 1 <= len(passes) <= n
+            assert passes[0][1] == len(rows) and passes[-1][0] == 0
+            assert all(a[0] == b[1] for a, b in zip(passes, passes[1:]))  # consecutive, descending
+            assert all(b % 4 == 0 for b, _ in passes)
+    assert level_passes(level_geometry(16, 2**19, 3, 16, 2048).rows, 2) == [(8, 16), (0, 8)]
+
+
+def test_pending_reduce_is_a_noop_without_a_process_group():
+    g = torch.ones(4)
+    pending = PendingReduce()
+    pending.start([g, None])
+    pending.finish()
+    assert torch.equal(g, torch.ones(4))
 
 
 def test_allreduce_is_a_noop_without_a_process_group():
@@ -55,6 +83,17 @@ def _worker(rank: int, world: int, port: int, results):
         total = sum(range(1, world + 1))
         assert torch.all(big == total) and torch.all(other == total) and torch.all(strided == total)
         assert torch.all(small[0] == sum(range(world))) and torch.all(small[1] == 2.0 * sum(range(world)))
+
+        # 1b. the same sums started asynchronously, range by range, and awaited once
+        table = torch.full((1000, 2), float(rank + 1))
+        tiny = [torch.full((5,), float(rank)), torch.full((2, 3), 3.0 * rank)]
+        pending = PendingReduce(bucket_bytes=1 << 12)
+        pending.start(tiny)
+        pending.start([table[600:]])
+        pending.start([table[:600]])
+        pending.finish()
+        assert torch.all(table == total)
+        assert torch.all(tiny[0] == sum(range(world))) and torch.all(tiny[1] == 3.0 * sum(range(world)))
 
         # 2. data parallel identity with the CPU port of the training step: mean-loss gradients of the
         #    two half batches, summed and halved, equal the full-batch gradient

@@ -93,6 +93,33 @@ def test_training_step_tracks_the_cpu_port():
     assert float((got.float().cpu() - want).abs().max() / want.abs().max()) <= 1e-2
 
 
+def test_backward_in_level_passes_matches_the_autograd_path():
+    # the backward a multi-rank run may take (encoding backward range by range, sums started in
+    # between), here on one rank where the sums are no-ops: same gradients as the single-pass backward
+    torch.manual_seed(3)
+    enc = HashEncoding(2**12, 8, 3, 2, 8, 128)
+    mlp = FullyFusedMLP(16, 32, 4, depth=2, bias=False)
+    trainer = NeuralFieldTrainer(enc.cuda().half(), mlp.cuda().half(), lr=1e-2)
+    g = torch.Generator().manual_seed(4)
+    coords = torch.rand(8192, 3, generator=g).cuda()
+    targets = torch.rand(8192, 4, generator=g).cuda().half()
+
+    def grads(run):
+        for p in trainer.parameters():
+            p.grad = None
+        _, loss_sum = run()
+        return float(loss_sum), {n: p.grad.float().clone() for n, p in trainer.named_parameters()}
+
+    loss_a, plain = grads(lambda: trainer._backward_through_autograd(coords, targets))
+    for passes in (1, 2, 4):
+        loss_b, ranged = grads(lambda: trainer._backward_in_level_passes(coords, targets, passes))
+        assert abs(loss_a - loss_b) <= 1e-4 * abs(loss_a)  # the squared errors are summed with float atomics
+        for name in plain:
+            # float16 reductions arrive in a different order from run to run
+            err = float((plain[name] - ranged[name]).abs().max() / plain[name].abs().max())
+            assert err <= 2e-2, f"{name}: {err}"
+
+
 # ---- measurement entry points ---------------------------------------------------------------------
 
 

@@ -117,6 +117,61 @@ class _Launch:
         )
 
 
+def _launch_backward(launch: "_Launch", do: Tensor, de: Tensor, D_in: int, D_embed: int, levels: int, begin: int, end: int):
+    r"""``th_hash_bwd`` for levels ``[begin, end)``: adds into the (zero-initialised) table gradient ``de``."""
+    D_out = do.shape[-1]
+    go = _flatten_rows(do, D_out)
+    if go.dtype != de.dtype:
+        go = go.to(de.dtype)
+    if go.stride(-1) != 1 or (go.shape[0] > 1 and go.stride(0) < D_out):
+        go = go.contiguous()  # e.g. the stride-0 gradient of ``o.sum()``
+    go_stride = go.stride(0) if go.shape[0] > 1 else D_out
+    device = de.device
+    with torch.cuda.device(device):
+        _lib.check(
+            _lib.lib().th_hash_bwd(
+                *launch.coord_args, go.data_ptr(), go_stride, de.data_ptr(), _lib.dtype_code(de),
+                launch.n, D_in, D_embed, levels, launch.res, launch.rows, launch.offsets, launch.primes,
+                launch.scale, begin, end, _lib.stream_ptr(device),
+            ),
+            "th_hash_bwd",
+        )  # fmt: skip
+
+
+@torch.no_grad()
+def hash_encoding_backward_levels(
+    coord: Tensor,
+    grad_out: Tensor,
+    grad_embeddings: Tensor,
+    pi: Optional[Tensor],
+    max_entries_per_level: int,
+    min_res: int,
+    max_res: int,
+    levels: int,
+    level_begin: int,
+    level_end: int,
+    scale: float = 1.0,
+) -> None:
+    r"""Adds the table gradient of levels ``[level_begin, level_end)`` into ``grad_embeddings``.
+
+    The piece of ``HashEncoding.backward`` that a caller needs when it wants the gradient level range
+    by level range, e.g. to start summing the finished rows over ranks while the other levels are
+    still being computed (``training.NeuralFieldTrainer``).  ``grad_out`` is the gradient of the
+    encoding's output (its first ``levels * F`` columns are read), ``grad_embeddings`` a tensor shaped
+    and typed like the table that starts at zero.  triton_helpers has no such entry: its backward
+    always returns the whole table gradient (hash_encoding/kernel.py:636-671).
+    """
+    D_in, D_embed = coord.shape[-1], grad_embeddings.shape[-1]
+    if pi is None:
+        pi = _default_pi(coord.device)
+    _lib.require_cuda(coord, grad_out, grad_embeddings, pi)
+    assert 0 <= level_begin < level_end <= levels, "level range out of bounds"
+    assert grad_embeddings.is_contiguous(), "the table gradient must be contiguous"
+    launch = _Launch(coord, pi, D_in, max_entries_per_level, levels, min_res, max_res, scale)
+    assert grad_embeddings.shape[0] >= launch.geo.total_rows
+    _launch_backward(launch, grad_out, grad_embeddings, D_in, D_embed, levels, level_begin, level_end)
+
+
 class HashEncoding(torch.autograd.Function):
 
     @staticmethod
@@ -213,28 +268,9 @@ class HashEncoding(torch.autograd.Function):
 
         launch = _Launch(coords, ctx.prime_values, D_in, ctx.max_entries_per_level, levels, ctx.min_res, ctx.max_res, ctx.scale)
         de = torch.zeros(embeddings.shape, dtype=embeddings.dtype, device=embeddings.device)
-
-        D_out = do.shape[-1]
-        go = _flatten_rows(do, D_out)
-        if go.dtype != de.dtype:
-            go = go.to(de.dtype)
-        if go.stride(-1) != 1 or (go.shape[0] > 1 and go.stride(0) < D_out):
-            go = go.contiguous()  # e.g. the stride-0 gradient of ``o.sum()``
-        go_stride = go.stride(0) if go.shape[0] > 1 else D_out
-
         step = ctx.bwd_divider if ctx.bwd_divider is not None else levels
-        device = embeddings.device
-        with torch.cuda.device(device):
-            stream = _lib.stream_ptr(device)
-            for begin in range(0, levels, step):
-                _lib.check(
-                    _lib.lib().th_hash_bwd(
-                        *launch.coord_args, go.data_ptr(), go_stride, de.data_ptr(), _lib.dtype_code(de),
-                        launch.n, D_in, D_embed, levels, launch.res, launch.rows, launch.offsets, launch.primes,
-                        launch.scale, begin, begin + step, stream,
-                    ),
-                    "th_hash_bwd",
-                )  # fmt: skip
+        for begin in range(0, levels, step):
+            _launch_backward(launch, do, de, D_in, D_embed, levels, begin, begin + step)
         return None, de, None, None, None, None, None, None, None, None, None
 
     @staticmethod

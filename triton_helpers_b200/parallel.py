@@ -91,3 +91,64 @@ def allreduce_gradients(
             for m in members:
                 m.copy_(flat[offset : offset + m.numel()].view_as(m))
                 offset += m.numel()
+
+
+def level_passes(level_rows: Sequence[int], n_passes: int, align: int = 4) -> List[Tuple[int, int]]:
+    r"""Cuts levels ``0 .. len(level_rows)`` into at most ``n_passes`` consecutive ranges holding about
+    equal numbers of table rows, with boundaries at multiples of ``align`` levels (the backward kernel
+    handles four levels per register group), listed FINEST FIRST: the fine levels hold most rows, so
+    their all-reduce is the one worth starting early."""
+    levels = len(level_rows)
+    if n_passes <= 1 or levels <= align:
+        return [(0, levels)]
+    total = sum(level_rows)
+    cuts, acc, target = [], 0, total / n_passes
+    for l in range(levels - 1, 0, -1):  # walk down from the finest level
+        acc += level_rows[l]
+        if l % align == 0 and acc >= target * (len(cuts) + 1) and len(cuts) < n_passes - 1:
+            cuts.append(l)
+    bounds = [levels] + cuts + [0]
+    return [(bounds[i + 1], bounds[i]) for i in range(len(bounds) - 1)]
+
+
+class PendingReduce:
+    r"""Sums of gradient tensors over all ranks that have been started and not yet awaited.
+
+    ``start`` queues an asynchronous all-reduce of each tensor (small tensors of one dtype share a flat
+    buffer, as in ``allreduce_gradients``) behind the work already queued on the current stream;
+    ``finish`` makes the current stream wait for all of them and copies flat buffers back.  Between
+    the two the caller keeps launching kernels that do not touch those tensors."""
+
+    def __init__(self, group: Optional[dist.ProcessGroup] = None, bucket_bytes: int = 1 << 20):
+        self.group, self.bucket_bytes = group, bucket_bytes
+        self.active = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+        self._works = []
+        self._unpack = []
+
+    def start(self, grads: Iterable[Tensor]) -> None:
+        if not self.active:
+            return
+        grads = [g for g in grads if g is not None]
+        by_dtype = {}
+        for g in grads:
+            by_dtype.setdefault(g.dtype, []).append(g)
+        for same in by_dtype.values():
+            sizes = [g.numel() * g.element_size() for g in same]
+            for bucket in plan_buckets(sizes, self.bucket_bytes):
+                members = [same[i] for i in bucket]
+                if len(members) == 1 and members[0].is_contiguous():
+                    self._works.append(dist.all_reduce(members[0], op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+                    continue
+                flat = torch.cat([m.reshape(-1) for m in members])
+                self._works.append(dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+                self._unpack.append((flat, members))
+
+    def finish(self) -> None:
+        for work in self._works:
+            work.wait()
+        for flat, members in self._unpack:
+            offset = 0
+            for m in members:
+                m.copy_(flat[offset : offset + m.numel()].view_as(m))
+                offset += m.numel()
+        self._works, self._unpack = [], []

@@ -18,8 +18,10 @@ from torch import Tensor
 from . import _lib
 from .layers.fully_fused_mlp import FullyFusedMLP
 from .layers.hash_encoding import HashEncoding
+from .layers.hash_encoding.helpers import level_geometry
+from .layers.hash_encoding.kernel import hash_encoding_backward_levels
 from .optim import FusedAdam
-from .parallel import allreduce_gradients
+from .parallel import PendingReduce, allreduce_gradients, level_passes
 
 
 @torch.no_grad()
@@ -53,6 +55,14 @@ class NeuralFieldTrainer(nn.Module):
             gradient, i.e. the loss is scaled so 16-bit gradients neither underflow nor overflow;
             Adam undoes the scale exactly.
         group: process group for data parallelism (``None``: the default group, if initialised).
+        backward_passes: ``None`` (default): one backward through autograd, then one gradient sum over
+            the ranks.  An integer n: the encoding backward runs in n level ranges, finest first; the
+            gradient rows of a finished range are summed over the ranks (NCCL, asynchronously) while
+            the kernels of the next range run, and the MLP gradients are summed under the whole
+            encoding backward.  Measured on 2 B200 with the cfg 3 step: 2.08 ms per step with n = 2
+            against 2.07 ms without - the sum of 24 MB over NVLink takes about as long as the second
+            pass over the points costs extra - so overlapping is left to the caller to switch on
+            (slower interconnects, larger tables).
     """
 
     def __init__(
@@ -64,12 +74,14 @@ class NeuralFieldTrainer(nn.Module):
         eps: float = 1e-15,
         grad_out_scale: float = 1.0 / 16.0,
         group: Optional[dist.ProcessGroup] = None,
+        backward_passes: Optional[int] = None,
     ):
         super().__init__()
         self.encoding = encoding
         self.mlp = mlp
         self.grad_out_scale = grad_out_scale
         self.group = group
+        self.backward_passes = backward_passes
         self.optimizer = FusedAdam(self.parameters(), lr=lr, betas=betas, eps=eps)
 
     def world_size(self) -> int:
@@ -82,15 +94,50 @@ class NeuralFieldTrainer(nn.Module):
     def step(self, coords: Tensor, targets: Tensor) -> Tensor:
         r"""One optimisation step on this rank's points; returns the local mean squared error
         (float32, on the device, not synchronised)."""
-        pred = self.forward(coords)
-        grad_out, loss_sum = mse_grad(pred, targets.to(pred.dtype), self.grad_out_scale)
-        pred.backward(grad_out)
         world = self.world_size()
-        grads = [p.grad for p in self.parameters() if p.grad is not None]
-        allreduce_gradients(grads, self.group)
+        passes = self.backward_passes
+        if passes is None:
+            pred, loss_sum = self._backward_through_autograd(coords, targets)
+        else:
+            pred, loss_sum = self._backward_in_level_passes(coords, targets, passes)
         # d(mean over the global batch)/d pred = 2 (pred - target) / (N_global * C)
         true_over_stored = 2.0 / (pred.numel() * world * self.grad_out_scale)
         self.optimizer.step(grad_scale=true_over_stored)
         for p in self.parameters():
             p.grad = None
         return loss_sum / pred.numel()
+
+    def _backward_through_autograd(self, coords: Tensor, targets: Tensor) -> Tuple[Tensor, Tensor]:
+        pred = self.forward(coords)
+        grad_out, loss_sum = mse_grad(pred, targets.to(pred.dtype), self.grad_out_scale)
+        pred.backward(grad_out)
+        allreduce_gradients([p.grad for p in self.parameters() if p.grad is not None], self.group)
+        return pred, loss_sum
+
+    def _backward_in_level_passes(self, coords: Tensor, targets: Tensor, n_passes: int) -> Tuple[Tensor, Tensor]:
+        r"""The same gradients with the exchange overlapped: autograd covers the MLP only; the encoding
+        backward is launched range by range (finest levels first) and each finished range of table
+        rows goes to an asynchronous all-reduce while the next range is computed."""
+        enc = self.encoding
+        with torch.no_grad():
+            feats = enc(coords)
+        feats.requires_grad_(True)
+        pred = self.mlp(feats.unsqueeze(0)).squeeze(0)
+        grad_out, loss_sum = mse_grad(pred, targets.to(pred.dtype), self.grad_out_scale)
+        pred.backward(grad_out)
+        pending = PendingReduce(self.group)
+        pending.start([p.grad for p in self.mlp.parameters() if p.grad is not None])
+        table = enc.embeddings
+        geo = level_geometry(enc.num_levels, enc.max_entries_per_level, coords.shape[-1], enc.min_res, enc.max_res)
+        grad_table = torch.zeros_like(table)
+        for begin, end in level_passes(geo.rows, n_passes):
+            hash_encoding_backward_levels(
+                coords, feats.grad, grad_table, enc.pi, enc.max_entries_per_level, enc.min_res, enc.max_res,
+                enc.num_levels, begin, end,
+            )  # fmt: skip
+            first_row = geo.offsets[begin]
+            last_row = geo.offsets[end - 1] + geo.rows[end - 1]
+            pending.start([grad_table[first_row:last_row]])
+        pending.finish()
+        table.grad = grad_table
+        return pred, loss_sum
