@@ -403,8 +403,9 @@ def timed_region(fn, steps, world):
 
 def l2_probe(device):
     r"""What the L2 delivers for the encoding's two access patterns, measured with ``th_probe_l2`` on a
-    24 MB buffer (the size of the cfg 3 float16 table): coalesced streaming reads in GB/s and
-    random 32-byte-sector gathers in 1e9 per second.  CUDA events on the launching stream."""
+    24 MB buffer (the size of the cfg 3 float16 table): coalesced streaming reads in GB/s, random
+    32-byte-sector gathers and random float16-pair reductions in 1e9 per second.  CUDA events on the
+    launching stream."""
     import ctypes
 
     from triton_helpers_b200 import _lib
@@ -413,7 +414,7 @@ def l2_probe(device):
     sink = torch.zeros(1, dtype=torch.int32, device=device)
     lib, stream = _lib.lib(), _lib.stream_ptr(device)
     out = {}
-    for mode, iters, key, scale in ((0, 40, "stream_gbs", 1e9), (1, 64, "gather_g_per_s", 1e9)):
+    for mode, iters, key, scale in ((0, 40, "stream_gbs", 1e9), (1, 64, "gather_g_per_s", 1e9), (2, 64, "update_g_per_s", 1e9)):
         work = ctypes.c_int64(0)
         call = lambda: _lib.check(lib.th_probe_l2(buf.data_ptr(), buf.numel(), mode, iters, sink.data_ptr(), ctypes.byref(work), stream), "th_probe_l2")  # noqa: E731
         for _ in range(3):
@@ -529,6 +530,10 @@ def main():
         if fwd and hasattr(wl, "gathers_per_step"):
             l2["hash_fwd_gather_g_per_s"] = wl.gathers_per_step * args.steps / (fwd[1] * 1e-3) / 1e9
             l2["hash_fwd_frac_of_gather_probe"] = l2["hash_fwd_gather_g_per_s"] / l2["gather_g_per_s"]
+        bwd = kernels.get("th_hash_bwd")
+        if bwd and hasattr(wl, "gathers_per_step"):
+            l2["hash_bwd_update_g_per_s"] = wl.gathers_per_step * args.steps / (bwd[1] * 1e-3) / 1e9
+            l2["hash_bwd_frac_of_update_probe"] = l2["hash_bwd_update_g_per_s"] / l2["update_g_per_s"]
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload == "train_step":

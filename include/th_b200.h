@@ -253,8 +253,10 @@ int th_adam_step(void *param_dev, void *grad_dev, float *exp_avg_dev, float *exp
  * Measurement aid (no counterpart in triton_helpers): reads of an L2-resident buffer in the two
  * patterns the hash encoding makes.  mode 0: coalesced 16-byte streaming reads, `iters` passes over
  * the buffer; mode 1: 4-byte reads from pseudo-random 32-byte sectors, eight in flight per thread,
- * `iters` rounds.  *work_out_host receives the bytes read (mode 0) or the number of gathers (mode 1)
- * of the launch; the caller times it with CUDA events.  `sink_dev` is a 4-byte device scratch word.
+ * `iters` rounds; mode 2: the same pattern with float16-pair reductions instead of reads (the buffer's
+ * contents are overwritten).  *work_out_host receives the bytes read (mode 0) or the number of
+ * gathers / updates (modes 1, 2) of the launch; the caller times it with CUDA events.  `sink_dev` is
+ * a 4-byte device scratch word.
  * ------------------------------------------------------------------------------------------ */
 int th_probe_l2(const void *buffer_dev, int64_t n_bytes, int mode, int iters, void *sink_dev, int64_t *work_out_host,
                 void *stream);

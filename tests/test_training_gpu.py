@@ -131,15 +131,15 @@ def test_launch_counter_and_l2_probe():
     buf = torch.zeros(8 * 2**20, dtype=torch.uint8, device=device)
     sink = torch.zeros(1, dtype=torch.int32, device=device)
     before = lib.th_launch_count()
-    for mode, expect in ((0, 8 * 2**20 * 3), (1, None)):
+    for mode, expect in ((0, 8 * 2**20 * 3), (1, None), (2, None)):
         work = ctypes.c_int64(0)
         _lib.check(lib.th_probe_l2(buf.data_ptr(), buf.numel(), mode, 3, sink.data_ptr(), ctypes.byref(work), _lib.stream_ptr(device)), "th_probe_l2")
         assert work.value > 0 and (expect is None or work.value == expect)
     torch.cuda.synchronize()
-    assert lib.th_launch_count() - before == 2
+    assert lib.th_launch_count() - before == 3
     # argument errors are reported, not launched
     assert lib.th_probe_l2(buf.data_ptr(), buf.numel(), 7, 1, sink.data_ptr(), None, _lib.stream_ptr(device)) < 0
-    assert lib.th_launch_count() - before == 2
+    assert lib.th_launch_count() - before == 3
 
 
 def test_no_stream_synchronisation_in_the_encoding_calls():

@@ -317,13 +317,20 @@ struct SlotBarriers {
     unsigned long long acc_full[kMaxSlots];
 };
 
-// a poll that does not succeed comes back after a few microseconds: 2^16 of them are a fraction of a
-// second, orders of magnitude above any wait of a healthy run
-constexpr int kPipeWaitPolls = 1 << 16;
+// Bounded by wall-clock time (the nanosecond global timer, looked at every 64 polls): two seconds are
+// orders of magnitude above any wait of a healthy run, also under a profiler's replay.
+constexpr unsigned long long kPipeWaitNs = 2000000000ull;
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ bool pipe_wait(uint32_t bar, uint32_t parity, int *abort_flag) {
     if (*reinterpret_cast<volatile int *>(abort_flag)) return false;
-    for (int poll = 0; poll < kPipeWaitPolls; ++poll) {
+    unsigned long long deadline = 0;
+    for (unsigned poll = 0;; ++poll) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
@@ -331,7 +338,12 @@ __device__ __forceinline__ bool pipe_wait(uint32_t bar, uint32_t parity, int *ab
             : "r"(bar), "r"(parity)
             : "memory");
         if (done) return true;
-        if ((poll & 63) == 63 && *reinterpret_cast<volatile int *>(abort_flag)) return false;
+        if ((poll & 63u) == 63u) {
+            if (*reinterpret_cast<volatile int *>(abort_flag)) return false;
+            const unsigned long long now = global_ns();
+            if (deadline == 0) deadline = now + kPipeWaitNs;
+            else if (now > deadline) break;
+        }
     }
     *reinterpret_cast<volatile int *>(abort_flag) = 1;
     g_tc_status = 1;

@@ -5,10 +5,13 @@
 //   mode 0  streaming reads : every thread walks the buffer in 16-byte steps, coalesced
 //   mode 1  sector gathers  : every thread reads 4 bytes from pseudo-random 32-byte sectors, eight
 //                             independent loads in flight (the eight corners of a grid cell)
+//   mode 2  sector updates  : every thread adds a packed half pair (red.global.add.noftz.f16x2) to
+//                             4 bytes of pseudo-random 32-byte sectors, eight per round: the
+//                             encoding backward's access pattern with no arithmetic around it
 //
 // With a buffer of a few tens of MB and a warm-up pass the data comes from L2.  The caller times the
 // launch with CUDA events and divides: bytes = n_bytes * iters (mode 0), gathers = threads * 8 * iters
-// (mode 1, returned through *work_out).
+// (modes 1 and 2, returned through *work_out).  Mode 2 overwrites the buffer's contents.
 #include "common.cuh"
 
 namespace th {
@@ -47,6 +50,20 @@ __global__ void __launch_bounds__(kProbeThreads) l2_gather_kernel(const unsigned
     if (acc == 0x9e3779b9u) *sink = acc;
 }
 
+__global__ void __launch_bounds__(kProbeThreads) l2_update_kernel(unsigned *__restrict__ buf, unsigned n_sectors, int iters) {
+    unsigned state = (blockIdx.x * kProbeThreads + threadIdx.x) * 2654435761u + 12345u;
+    const unsigned one_pair = 0x14001400u;  // two small float16 values
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            state = state * 1664525u + 1013904223u;
+            const unsigned sector = static_cast<unsigned>((static_cast<unsigned long long>(state) * n_sectors) >> 32);
+            asm volatile("red.global.add.noftz.f16x2 [%0], %1;" ::"l"(buf + static_cast<size_t>(sector) * 8 + (state & 7u)), "r"(one_pair)
+                         : "memory");
+        }
+    }
+}
+
 }  // namespace
 }  // namespace th
 
@@ -55,7 +72,7 @@ extern "C" int th_probe_l2(const void *buffer, int64_t n_bytes, int mode, int it
     using namespace th;
     if (!buffer || !sink || n_bytes < 4096 || iters < 1) return fail(TH_ERR_BAD_ARG, "th_probe_l2: buffer, sink, n_bytes >= 4096 and iters >= 1 are required");
     if (!aligned_to(buffer, 16)) return fail(TH_ERR_ALIGNMENT, "th_probe_l2: buffer must be 16-byte aligned");
-    if (mode != 0 && mode != 1) return fail(TH_ERR_BAD_ARG, "th_probe_l2: mode is 0 (stream) or 1 (gather)");
+    if (mode < 0 || mode > 2) return fail(TH_ERR_BAD_ARG, "th_probe_l2: mode is 0 (stream), 1 (gather) or 2 (update)");
     const int ctas = sm_count() * kProbeCtasPerSm;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (mode == 0) {
@@ -64,8 +81,12 @@ extern "C" int th_probe_l2(const void *buffer, int64_t n_bytes, int mode, int it
         if (work_out) *work_out = n_vec * 16 * iters;
     } else {
         if (n_bytes / 32 > 0xffffffffll) return fail(TH_ERR_BAD_ARG, "th_probe_l2: buffer too large for the gather probe");
-        l2_gather_kernel<<<ctas, kProbeThreads, 0, s>>>(static_cast<const unsigned *>(buffer), static_cast<unsigned>(n_bytes / 32), iters,
-                                                        static_cast<unsigned *>(sink));
+        if (mode == 1)
+            l2_gather_kernel<<<ctas, kProbeThreads, 0, s>>>(static_cast<const unsigned *>(buffer), static_cast<unsigned>(n_bytes / 32),
+                                                            iters, static_cast<unsigned *>(sink));
+        else
+            l2_update_kernel<<<ctas, kProbeThreads, 0, s>>>(static_cast<unsigned *>(const_cast<void *>(buffer)),
+                                                            static_cast<unsigned>(n_bytes / 32), iters);
         if (work_out) *work_out = static_cast<int64_t>(ctas) * kProbeThreads * 8 * iters;
     }
     return launch_status("th_probe_l2 launch");
