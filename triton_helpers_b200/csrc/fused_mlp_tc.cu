@@ -951,7 +951,10 @@ mlp_bwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
             auto act_addr = [&](int l) { return smem_base + static_cast<uint32_t>((base + l) % n_act) * kTileBytes; };
             // ---- phase 1 ----
             for (int l = 0; l < d; ++l) {
-                if (wait_acc()) {
+                TH_STAMP(80);
+                const bool ok1 = wait_acc();
+                TH_STAMP(81);
+                if (ok1) {
                     const int n = s.h / kGroups;  // this thread's columns
                     const uint32_t dst = act_addr(l + 1) + row_off;
                     const int first = seat.group * (n / 8);
@@ -959,12 +962,15 @@ mlp_bwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
                         st_shared_16(dst + (((first + u) << 4) ^ row_swizzle), finish8<T, ACT, false>(piece, nullptr));
                     });
                 }
+                TH_STAMP(82);
                 publish();
             }
             // ---- phase 2 ----
             for (int l = d; l >= 0; --l) {
                 const int in_pad = l == 0 ? s.ki : s.h;
+                TH_STAMP(83);
                 const bool ok = wait_acc();
+                TH_STAMP(84);
                 const int n = in_pad / kGroups;
                 const int first = seat.group * (n / 8);
                 if (ok && l > 0) {
@@ -989,6 +995,7 @@ mlp_bwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
                         if (live) store_chunk_to_global<T>(row_ptr, first + u, s.d_in, finish8<T, TH_ACT_NONE, false>(piece, nullptr), gx_vec);
                     });
                 }
+                TH_STAMP(85);
                 publish();
             }
             if (d > 0) {
