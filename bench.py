@@ -141,7 +141,7 @@ class TrainStep:
     name = "cfg3: 2^21 pts/GPU, hash L16 F2 T2^19 16..2048 fp16 -> MLP 32-64-64-16 fp16 -> MSE -> allreduce -> Adam"
     dtype = "f16"
 
-    def __init__(self, device, rank, points):
+    def __init__(self, device, rank, points, backward_passes=None):
         from triton_helpers_b200.layers.fully_fused_mlp import FullyFusedMLP
         from triton_helpers_b200.layers.hash_encoding import HashEncoding
         from triton_helpers_b200.training import NeuralFieldTrainer
@@ -152,7 +152,8 @@ class TrainStep:
         with torch.no_grad():
             enc.embeddings.uniform_(-1e-4, 1e-4)
         mlp = FullyFusedMLP(32, 64, 16, depth=2, bias=False)
-        self.trainer = NeuralFieldTrainer(enc.to(device).half(), mlp.to(device).half(), lr=1e-2, betas=(0.9, 0.99), eps=1e-15)
+        self.trainer = NeuralFieldTrainer(enc.to(device).half(), mlp.to(device).half(), lr=1e-2, betas=(0.9, 0.99), eps=1e-15,
+                                          backward_passes=backward_passes)
         gen = torch.Generator(device=device).manual_seed(1234 + rank)  # a different batch per rank
         self.coords = torch.rand(points, 3, device=device, generator=gen)
         self.targets = torch.rand(points, 16, device=device, generator=gen).half()
@@ -290,9 +291,9 @@ class ReversibleOnly:
 
 
 
-def build_workload(name, device, rank):
+def build_workload(name, device, rank, backward_passes=None):
     if name == "train_step":
-        return TrainStep(device, rank, 2**21)
+        return TrainStep(device, rank, 2**21, backward_passes)
     if name in HASH_CFG:
         return HashOnly(device, rank, name)
     if name == "mlp":
@@ -438,6 +439,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="train_step", choices=["train_step", "hash", "mlp", "reversible", "contention"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--backward-passes", type=int, default=None,
+                    help="train_step: run the encoding backward in this many level ranges with the gradient sums overlapped")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="time CUDA-graph replays of the step (auto: single-operator workloads on one GPU)")
     args = ap.parse_args()
@@ -458,7 +461,7 @@ def main():
     device = torch.device("cuda", local_rank)
     _lib.lib()  # fail loudly here if the extension is missing
 
-    wl = build_workload(args.workload, device, rank)
+    wl = build_workload(args.workload, device, rank, args.backward_passes)
     # the sampler starts before the warm-up (nvidia-smi takes ~100 ms to deliver its first line);
     # the busier half of its samples is what gets summarised
     use_graph = args.graph == "on" or (args.graph == "auto" and world == 1 and args.workload != "train_step")
