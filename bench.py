@@ -41,7 +41,7 @@ METRIC = "fwd+bwd points/sec (hash-enc + fused MLP)"
 # mlp_fwd_pipe_kernel_cfg3.md), all taken on the full cfg 3 workload; th_hash_bwd is the sum of its two
 # kernels.  Other workloads have no capture yet: traffic is reported as null there.
 NCU_TRAFFIC_BYTES = {
-    "train_step": {"th_hash_bwd": 355.9e6, "th_hash_fwd": 131.4e6, "th_mlp_bwd": 292.4e6, "th_mlp_fwd": 174.6e6},
+    "train_step": {"th_hash_bwd": 355.9e6, "th_hash_fwd": 131.4e6, "th_mlp_bwd": 292.4e6, "th_mlp_fwd": 174.6e6, "th_mlp_fwd_mse": None},
 }
 L2_BYTES = 126 * 1024 * 1024
 
@@ -201,6 +201,7 @@ class TrainStep:
             "th_hash_fwd": ("hbm", hash_bytes_per_point(16, 2, S) * n),
             "th_hash_bwd": ("hbm", hash_bytes_per_point(16, 2, S) * n),
             "th_mlp_fwd": ("tensor", mlp_flops * n),
+            "th_mlp_fwd_mse": ("tensor", mlp_flops * n),  # forward with the loss fused into its last layer
             "th_mlp_bwd": ("tensor", 2 * mlp_flops * n),
             "th_mse_grad": ("hbm", 3 * S * 16 * n),
             "th_adam_step": ("hbm", (3 * S + 16) * self.table_elems),

@@ -139,6 +139,18 @@ int th_mlp_fwd(const void *x_dev, int64_t x_stride, const void *w_in_dev, const 
                void *out_dev, int64_t out_stride, int64_t rows, int d_in, int d_hidden, int d_out, int depth,
                int activation, int dtype, int fp16_acc, void *stream);
 
+/* Forward with the squared-error loss fused into the output layer (no counterpart in triton_helpers;
+ * the step of a training loop that follows _fully_fused_mlp.forward): grad[r, c] = (y[r, c] -
+ * target[r, c]) * grad_scale in `dtype`, with y rounded to `dtype` first, and sum (y - target)^2 added
+ * to *loss_sum_dev (fp32, caller-zeroed; may be null).  out_dev may be null when the prediction itself
+ * is not needed.  Returns TH_ERR_UNSUPPORTED when the case is outside the tensor-core forward kernel
+ * (d_in or d_out not multiples of 8, misaligned rows, float32): call th_mlp_fwd and th_mse_grad then. */
+int th_mlp_fwd_mse(const void *x_dev, int64_t x_stride, const void *w_in_dev, const void *b_in_dev,
+                   const void *w_hid_dev, const void *b_hid_dev, const void *w_out_dev, const void *b_out_dev,
+                   void *out_dev, int64_t out_stride, const void *target_dev, int64_t target_stride, void *grad_dev,
+                   int64_t grad_stride, float *loss_sum_dev, float grad_scale, int64_t rows, int d_in, int d_hidden,
+                   int d_out, int depth, int activation, int dtype, void *stream);
+
 /* Device-side status word of the tensor-core MLP kernels: 0 = fine, 1 = one of their bounded waits
  * ran out (the kernel then returned early and its results are invalid).  Synchronises the device.
  * No counterpart in the reference. */
@@ -258,7 +270,7 @@ int th_adam_step(void *param_dev, void *grad_dev, float *exp_avg_dev, float *exp
  * gathers / updates (modes 1, 2) of the launch; the caller times it with CUDA events.  `sink_dev` is
  * a 4-byte device scratch word.
  * ------------------------------------------------------------------------------------------ */
-int th_probe_l2(const void *buffer_dev, int64_t n_bytes, int mode, int iters, void *sink_dev, int64_t *work_out_host,
+int th_probe_l2(void *buffer_dev, int64_t n_bytes, int mode, int iters, void *sink_dev, int64_t *work_out_host,
                 void *stream);
 
 #ifdef __cplusplus

@@ -117,6 +117,8 @@ def test_backward_reference_shapes(dtype, activation, depth):
         (129, 64, 64, 64, 2, True, "relu"),
         (255, 17, 32, 33, 5, True, "relu2"),
         (513, 48, 16, 7, 2, False, "none"),
+        (600, 40, 64, 24, 2, False, "relu"),  # input padded to 48 columns: 24 per thread in the epilogues
+        (300, 40, 32, 40, 3, True, "relu"),
     ],
 )
 def test_forward_backward_shapes_against_oracle(dtype, rows, d_in, d_hid, d_out, depth, bias, activation):
@@ -311,3 +313,41 @@ def test_mma_sync_kernels_still_pass_when_selected():
            "reference_shapes or shapes_against_oracle or empty_batch"]  # fmt: skip
     done = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
     assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-2000:]
+
+
+# ---- forward fused with the squared-error loss -----------------------------------------------------
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize(
+    "rows,d_in,d_hid,d_out,depth",
+    [(2**17 + 5, 32, 64, 16, 2), (1000, 32, 64, 16, 4), (300, 16, 32, 8, 1), (257, 3, 16, 5, 2)],  # the last: fallback path
+)
+def test_forward_fused_with_mse_matches_the_two_kernels(dtype, rows, d_in, d_hid, d_out, depth):
+    from triton_helpers_b200.layers.fully_fused_mlp import fully_fused_mlp_mse
+    from triton_helpers_b200.training import mse_grad
+
+    p = make_params(d_in, d_hid, d_out, depth, dtype, bias=False, seed=rows)
+    g = torch.Generator().manual_seed(rows)
+    x = torch.randn(1, rows, d_in, generator=g).to(dtype).cuda()
+    target = torch.rand(1, rows, d_out, generator=g).to(dtype).cuda()
+    scale = 1.0 / 16.0
+
+    def leaves():
+        ws = [p["w_in"], p["w_out"], p["w_hid"]]
+        return x.clone().requires_grad_(True), [None if w is None else w.cuda().clone().requires_grad_(True) for w in ws]
+
+    xa, (wi, wo, wh) = leaves()
+    pred = fully_fused_mlp(xa, wi, None, wo, None, wh, None)
+    grad_out, loss_ref = mse_grad(pred, target, scale)
+    pred.backward(grad_out)
+    xb, (wi2, wo2, wh2) = leaves()
+    loss = fully_fused_mlp_mse(xb, wi2, wo2, wh2, target, scale)
+    loss.backward()
+    assert abs(float(loss) - float(loss_ref)) <= 1e-4 * abs(float(loss_ref))
+    # same prediction bits -> same gradient tensor into the same backward kernels; only the order of the
+    # floating-point reductions differs
+    assert nerr(xb.grad, xa.grad) <= 1e-3
+    for a, b in ((wi, wi2), (wo, wo2), (wh, wh2)):
+        if a is not None:
+            assert nerr(b.grad, a.grad) <= (2e-3 if dtype == torch.float16 else 1.6e-2)

@@ -18,6 +18,7 @@ LIB_PATH = Path(__file__).resolve().parent / "csrc" / "libth_b200.so"
 
 DTYPE_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 ACTIVATION_CODE = {"none": 0, "relu": 1, "silu": 2, "relu2": 3}
+TH_ERR_UNSUPPORTED = -2  # include/th_b200.h
 
 _I32P = ctypes.POINTER(c_int32)
 _I64P = ctypes.POINTER(c_int64)
@@ -45,6 +46,11 @@ SIGNATURES = {
         c_int,
         [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
          c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    ),
+    "th_mlp_fwd_mse": (
+        c_int,
+        [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
+         c_int64, c_void_p, c_int64, c_void_p, c_float, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     ),
     "th_mlp_workspace_bytes": (c_int64, [c_int, c_int, c_int, c_int]),
     "th_mlp_tc_status": (c_int, []),
@@ -92,7 +98,7 @@ class KernelTimer:
     queued.  ``summary()`` synchronises and returns ``{entry point: (calls, total ms)}``.
     """
 
-    LAUNCHING = ("th_hash_fwd", "th_hash_bwd", "th_mlp_fwd", "th_mlp_bwd", "th_rev_fwd", "th_rev_bwd",
+    LAUNCHING = ("th_hash_fwd", "th_hash_bwd", "th_mlp_fwd", "th_mlp_fwd_mse", "th_mlp_bwd", "th_rev_fwd", "th_rev_bwd",
                  "th_mse_grad", "th_adam_step")  # fmt: skip
 
     def __init__(self):

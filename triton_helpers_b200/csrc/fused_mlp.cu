@@ -451,6 +451,29 @@ extern "C" int th_mlp_fwd(const void *x_dev, int64_t x_stride, const void *w_in_
     }
 }
 
+extern "C" int th_mlp_fwd_mse(const void *x_dev, int64_t x_stride, const void *w_in_dev, const void *b_in_dev,
+                              const void *w_hid_dev, const void *b_hid_dev, const void *w_out_dev, const void *b_out_dev,
+                              void *out_dev, int64_t out_stride, const void *target_dev, int64_t target_stride,
+                              void *grad_dev, int64_t grad_stride, float *loss_sum_dev, float grad_scale, int64_t rows,
+                              int d_in, int d_hidden, int d_out, int depth, int activation, int dtype, void *stream) {
+    if (rows < 0) return fail(TH_ERR_BAD_ARG, "negative row count");
+    const bool has_bias = b_in_dev || b_hid_dev || b_out_dev;
+    MlpShape s;
+    if (int rc = make_shape(s, d_in, d_hidden, d_out, depth, activation, has_bias)) return rc;
+    MlpParams p{w_in_dev, w_hid_dev, w_out_dev, b_in_dev, b_hid_dev, b_out_dev};
+    if (int rc = check_params(s, p, has_bias)) return rc;
+    if (rows == 0) return TH_OK;
+    if (!x_dev || !target_dev || !grad_dev) return fail(TH_ERR_BAD_ARG, "null input, target or gradient");
+    if (x_stride < d_in || target_stride < d_out || grad_stride < d_out || (out_dev && out_stride < d_out))
+        return fail(TH_ERR_BAD_ARG, "row stride smaller than the row");
+    const MseArgs mse{target_dev, target_stride, grad_dev, grad_stride, loss_sum_dev, grad_scale};
+    const int rc = mlp_fwd_mse_tc(s, p, x_dev, x_stride, out_dev, out_stride, mse, rows, dtype, static_cast<cudaStream_t>(stream));
+    if (rc == kTcNotApplicable)
+        return fail(TH_ERR_UNSUPPORTED, "fused forward + MSE needs float16 / bfloat16 rows of whole 16-byte chunks "
+                                        "(d_in, d_out multiples of 8, aligned) and a network the multi-slot kernel holds");
+    return rc;
+}
+
 extern "C" int th_mlp_bwd(const void *x_dev, int64_t x_stride, const void *w_in_dev, const void *b_in_dev,
                           const void *w_hid_dev, const void *b_hid_dev, const void *w_out_dev, const void *b_out_dev,
                           const void *grad_out_dev, int64_t go_stride, void *grad_x_dev, int64_t gx_stride,

@@ -1,12 +1,11 @@
 // Fully fused MLP on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM).
 //
-// One CTA of 256 threads owns a 128-row tile at a time (M = 128 = the TMEM lanes); several CTAs
-// share an SM, so one CTA's epilogue overlaps another's MMAs.  Warp w reads TMEM lanes
-// 32 * (w % 4) .. + 31 (thread = lane = tile row) and, of those rows, the column half w / 4.  Every operand tile lives in
-// shared memory in ONE layout: rows 128 bytes apart (64 16-bit features), 16-byte chunk c of
-// row r stored at chunk position c ^ (r & 7), tile base 1024-byte aligned.  That is the
-// canonical 128-byte-swizzle layout of the tensor core, and the same bytes can be described
-// to it two ways:
+// A 128-row tile of the batch is the unit of work (M = 128 = the TMEM lanes; a thread that reads an
+// accumulator reads the TMEM lanes of its warp quarter, thread = lane = tile row).  Every operand
+// tile lives in shared memory in ONE layout: rows 128 bytes apart (64 16-bit features), 16-byte
+// chunk c of row r stored at chunk position c ^ (r & 7), tile base 1024-byte aligned.  That is the
+// canonical 128-byte-swizzle layout of the tensor core, and the same bytes can be described to it
+// two ways:
 //   K-major  (the row index is M or N, features are K)  - forward GEMMs, the A side of dgrad;
 //   MN-major (the row index is K, features are M or N)  - wgrad (K = the tile's 128 rows) and
 //            the weight side of dgrad (K = a layer's outputs, N = its inputs),
@@ -16,13 +15,20 @@
 //   dgrad   : ACC[128 x in]  = DZ_l[128 x out] . W_l          A K-major, B MN-major
 //   wgrad   : DW_l[out x in] += DZ_l^T[out x 128] . ACT_l     A, B MN-major, M = 64
 //
-// Thread 0 issues the MMAs and commits them to an mbarrier; all 256 threads wait on it, read
-// their half row of the accumulator with tcgen05.ld in 8-column pieces (one piece = one 16-byte
-// chunk of the next operand tile), apply bias / activation / ReLU mask on packed 16-bit pairs
-// and write the next operand tile straight back to shared memory (fence.proxy.async before the
-// tensor core reads it).  Weight gradients
-// stay in TMEM columns for the whole life of the CTA (wgrad MMAs accumulate tile after tile
-// and are never waited on individually) and leave once, at the end, as red.global.add.f32.
+// An elected lane issues the MMAs and commits them to an mbarrier; the epilogue threads read their
+// part of the accumulator row with tcgen05.ld, apply bias / activation / ReLU mask on packed 16-bit
+// pairs and write the next operand tile straight back to shared memory (fence.proxy.async before
+// the tensor core reads it).  Weight gradients stay in TMEM columns for the whole life of the CTA
+// (wgrad MMAs accumulate tile after tile) and leave once, at the end, as red.global.add.f32.
+//
+// Four kernels, in the order of the file:
+//   mlp_fwd_tc_kernel   one tile per CTA of 256 threads, several CTAs per SM; the forward for rows
+//                       TMA cannot describe
+//   mlp_fwd_pipe_kernel one CTA per SM, up to four independent 128-thread slots with a tile each in
+//                       flight, sharing the weights; input tiles by TMA - the usual forward
+//   mlp_bwd_tc_kernel   one tile per CTA of 256 threads; the backward when only one CTA fits an SM
+//   mlp_bwd_pipe_kernel 256 epilogue threads + an issuer warp, dgrad and wgrad committed separately,
+//                       the next tile's inputs prefetched by TMA - the usual backward
 //
 // Weights reach shared memory by TMA (cp.async.bulk.tensor.2d, one box per layer, 128-byte swizzle:
 // the box lands directly in the operand-tile layout, zero filled where a layer is narrower than its
@@ -160,27 +166,21 @@ __device__ void stage_all_weights(unsigned char *smem, const TcPlan &P, const Ml
 template <typename T, int ACT, bool BIAS>
 __device__ __forceinline__ void hidden_epilogue(uint32_t taddr, const Seat &seat, int pad, const float *bias,
                                                 unsigned char *next_tile) {
-    const int count = pad / (8 * kGroups), first = seat.group * count;
-    uint32_t raw[kMaxChunks][8];
-    load_pieces(taddr, first, count, raw);
-#pragma unroll
-    for (int u = 0; u < kMaxChunks; ++u)
-        if (u < count)
-            *reinterpret_cast<uint4 *>(chunk_ptr(next_tile, seat.row, first + u)) =
-                finish_piece<T, ACT, BIAS>(raw[u], bias + 8 * (first + u));
+    const int n = pad / kGroups, first = seat.group * (n / 8);  // this thread's columns / first 8-column piece
+    const uint32_t row_addr = smem_addr(next_tile) + seat.row * 128, row_swizzle = (seat.row & 7) << 4;
+    for_each_piece(taddr + seat.group * n, n, [&](int u, const uint32_t(&piece)[8]) {
+        st_shared_16(row_addr + (((first + u) << 4) ^ row_swizzle), finish8<T, ACT, BIAS>(piece, bias + 8 * (first + u)));
+    });
 }
 
 template <typename T, bool BIAS>
 __device__ __forceinline__ void output_epilogue(uint32_t taddr, const Seat &seat, int pad, const float *bias, T *row_ptr,
                                                 int cols, bool live, bool vector_ok) {
-    const int count = pad / (8 * kGroups), first = seat.group * count;
-    uint32_t raw[kMaxChunks][8];
-    load_pieces(taddr, first, count, raw);
-#pragma unroll
-    for (int u = 0; u < kMaxChunks; ++u)
-        if (u < count && live)
-            store_chunk_to_global<T>(row_ptr, first + u, cols, finish_piece<T, TH_ACT_NONE, BIAS>(raw[u], bias + 8 * (first + u)),
-                                     vector_ok);
+    const int n = pad / kGroups, first = seat.group * (n / 8);
+    for_each_piece(taddr + seat.group * n, n, [&](int u, const uint32_t(&piece)[8]) {
+        if (live)
+            store_chunk_to_global<T>(row_ptr, first + u, cols, finish8<T, TH_ACT_NONE, BIAS>(piece, bias + 8 * (first + u)), vector_ok);
+    });
 }
 
 template <typename T, int ACT, bool BIAS>
@@ -310,7 +310,7 @@ mlp_fwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
 // Every mbarrier wait is bounded and watches a shared abort flag; after an abort a slot keeps the
 // SAME sequence of named barriers (doing no work) so nobody is left waiting at one.
 
-constexpr int kMaxSlots = 6;
+constexpr int kMaxSlots = 4;
 
 struct SlotBarriers {
     unsigned long long in_full[kMaxSlots][2];
@@ -374,11 +374,27 @@ __device__ __forceinline__ void drain_row(uint32_t taddr, int out_pad, const flo
     }
 }
 
-template <typename T, int ACT, bool BIAS, int S>
+// One 16-byte chunk of a prediction row against the same chunk of the target row: the scaled difference
+// (rounded to T) and the sum of the eight squared differences.
+template <typename T>
+__device__ __forceinline__ uint4 mse_chunk(uint4 pred, uint4 target, float grad_scale, float &loss) {
+    const uint32_t pw[4] = {pred.x, pred.y, pred.z, pred.w}, tw[4] = {target.x, target.y, target.z, target.w};
+    uint32_t gw[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 a = unpack_pair<T>(pw[k]), b = unpack_pair<T>(tw[k]);
+        const float d0 = a.x - b.x, d1 = a.y - b.y;
+        loss += d0 * d0 + d1 * d1;
+        gw[k] = pack_pair<T>(d0 * grad_scale, d1 * grad_scale);
+    }
+    return make_uint4(gw[0], gw[1], gw[2], gw[3]);
+}
+
+template <typename T, int ACT, bool BIAS, int S, bool MSE>
 __global__ void __launch_bounds__(128 * S, 1)
 mlp_fwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ WeightMaps maps,
                     const __grid_constant__ CUtensorMap x_map, T *__restrict__ y, long long y_stride, long long n_rows,
-                    int y_vec) {
+                    int y_vec, const MseArgs mse) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint32_t tmem_holder;
@@ -446,6 +462,7 @@ mlp_fwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
     const uint32_t acc_bar = smem_addr(&bars.acc_full[slot]);
     unsigned char *buffers = smem + 2 * slot * kTileBytes;
     uint32_t acc_phase = 0;  // tracked by the issuer warp
+    float loss = 0.f;        // MSE: this thread's share of sum (prediction - target)^2
     TH_TRACE_BEGIN
 
     auto fetch_input = [&](int b, long long k) {  // by the issuer warp
@@ -505,10 +522,25 @@ mlp_fwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
                     fence_async_smem();
                 } else {
                     const bool live = row0 + row < n_rows;
-                    T *out_row = y + (live ? row0 + row : 0) * y_stride;
-                    drain_row<T, TH_ACT_NONE, BIAS>(taddr, out_pad, layer_bias, [&](int chunk, uint4 packed) {
-                        if (live) store_chunk_to_global<T>(out_row, chunk, s.d_out, packed, y_vec);
-                    });
+                    if constexpr (MSE) {
+                        // d_out is a multiple of 8 and all rows are 16-byte aligned here (checked by the launcher)
+                        const long long r = live ? row0 + row : 0;
+                        const T *target_row = static_cast<const T *>(mse.target) + r * mse.target_stride;
+                        T *grad_row = static_cast<T *>(mse.grad) + r * mse.grad_stride;
+                        T *out_row = y ? y + r * y_stride : nullptr;
+                        drain_row<T, TH_ACT_NONE, BIAS>(taddr, out_pad, layer_bias, [&](int chunk, uint4 packed) {
+                            if (live && 8 * chunk < s.d_out) {
+                                if (out_row) __stcs(reinterpret_cast<uint4 *>(out_row + 8 * chunk), packed);
+                                const uint4 t = __ldcs(reinterpret_cast<const uint4 *>(target_row + 8 * chunk));
+                                __stcs(reinterpret_cast<uint4 *>(grad_row + 8 * chunk), mse_chunk<T>(packed, t, mse.grad_scale, loss));
+                            }
+                        });
+                    } else {
+                        T *out_row = y + (live ? row0 + row : 0) * y_stride;
+                        drain_row<T, TH_ACT_NONE, BIAS>(taddr, out_pad, layer_bias, [&](int chunk, uint4 packed) {
+                            if (live) store_chunk_to_global<T>(out_row, chunk, s.d_out, packed, y_vec);
+                        });
+                    }
                 }
                 tc_fence_before();
             }
@@ -516,6 +548,12 @@ mlp_fwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
             slot_barrier(slot);
             TH_STAMP(46);
         }
+    }
+
+    if constexpr (MSE) {
+        // one atomic per warp for the whole kernel
+        for (int off = 16; off > 0; off >>= 1) loss += __shfl_xor_sync(0xffffffffu, loss, off);
+        if ((threadIdx.x & 31) == 0 && mse.loss_sum) atomicAdd(mse.loss_sum, loss);
     }
 
     // ---- teardown ----
@@ -532,35 +570,30 @@ mlp_fwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
 template <typename T, int ACT>
 __device__ __forceinline__ void dz_epilogue(uint32_t taddr, const Seat &seat, int pad, unsigned char *parked,
                                             unsigned char *dz_tile) {
-    const int count = pad / (8 * kGroups), first = seat.group * count;
-    uint32_t raw[kMaxChunks][8];
-    load_pieces(taddr, first, count, raw);
-#pragma unroll
-    for (int u = 0; u < kMaxChunks; ++u) {
-        if (u < count) {
-            uint4 g = finish_piece<T, TH_ACT_NONE, false>(raw[u], nullptr);
-            if constexpr (ACT == TH_ACT_RELU) {
-                const uint4 a = *reinterpret_cast<const uint4 *>(chunk_ptr(parked, seat.row, first + u));
-                g.x = keep_where_positive<T>(g.x, a.x);
-                g.y = keep_where_positive<T>(g.y, a.y);
-                g.z = keep_where_positive<T>(g.z, a.z);
-                g.w = keep_where_positive<T>(g.w, a.w);
-            }
-            *reinterpret_cast<uint4 *>(chunk_ptr(dz_tile, seat.row, first + u)) = g;
+    const int n = pad / kGroups, first = seat.group * (n / 8);
+    const uint32_t row_off = seat.row * 128, row_swizzle = (seat.row & 7) << 4;
+    const uint32_t parked_row = smem_addr(parked) + row_off, dz_row = smem_addr(dz_tile) + row_off;
+    for_each_piece(taddr + seat.group * n, n, [&](int u, const uint32_t(&piece)[8]) {
+        const uint32_t off = ((first + u) << 4) ^ row_swizzle;
+        uint4 g = finish8<T, TH_ACT_NONE, false>(piece, nullptr);
+        if constexpr (ACT == TH_ACT_RELU) {
+            const uint4 a = ld_shared_16(parked_row + off);
+            g.x = keep_where_positive<T>(g.x, a.x);
+            g.y = keep_where_positive<T>(g.y, a.y);
+            g.z = keep_where_positive<T>(g.z, a.z);
+            g.w = keep_where_positive<T>(g.w, a.w);
         }
-    }
+        st_shared_16(dz_row + off, g);
+    });
 }
 
 template <typename T>
 __device__ __forceinline__ void dx_epilogue(uint32_t taddr, const Seat &seat, int pad, T *row_ptr, int cols, bool live,
                                             bool vector_ok) {
-    const int count = pad / (8 * kGroups), first = seat.group * count;
-    uint32_t raw[kMaxChunks][8];
-    load_pieces(taddr, first, count, raw);
-#pragma unroll
-    for (int u = 0; u < kMaxChunks; ++u)
-        if (u < count && live)
-            store_chunk_to_global<T>(row_ptr, first + u, cols, finish_piece<T, TH_ACT_NONE, false>(raw[u], nullptr), vector_ok);
+    const int n = pad / kGroups, first = seat.group * (n / 8);
+    for_each_piece(taddr + seat.group * n, n, [&](int u, const uint32_t(&piece)[8]) {
+        if (live) store_chunk_to_global<T>(row_ptr, first + u, cols, finish8<T, TH_ACT_NONE, false>(piece, nullptr), vector_ok);
+    });
 }
 
 // Flush one layer's weight-gradient accumulator (M = 64 layout: gradient row m sits in TMEM lane
@@ -1120,9 +1153,9 @@ bool pipe_disabled() {
     return off;
 }
 
-template <typename T, int ACT, bool BIAS, int S>
+template <typename T, int ACT, bool BIAS, int S, bool MSE = false>
 int launch_fwd_pipe(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, void *y, int64_t y_stride,
-                    int64_t rows, cudaStream_t stream) {
+                    int64_t rows, cudaStream_t stream, const MseArgs &mse = MseArgs{}) {
     const TcPlan P = tc_plan(s, false, 2 * S);
     const int smem = P.total + 1024;
     if (smem > kSmemBudget || pipe_disabled()) return kTcNotApplicable;
@@ -1131,33 +1164,38 @@ int launch_fwd_pipe(const MlpShape &s, const MlpParams &p, const void *x, int64_
     CUtensorMap x_map;
     if (!make_weight_maps(maps, s, p)) return kTcNotApplicable;
     if (!make_map(&x_map, x, rows, s.d_in, kTileRows, x_stride)) return kTcNotApplicable;
-    auto kernel = mlp_fwd_pipe_kernel<T, ACT, BIAS, S>;
+    auto kernel = mlp_fwd_pipe_kernel<T, ACT, BIAS, S, MSE>;
     if (int rc = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
                              "cudaFuncSetAttribute(mlp_fwd_pipe_kernel)")) return rc;
     const long long tiles = (rows + kTileRows - 1) / kTileRows;
     const long long cap = sm_count();
     kernel<<<static_cast<unsigned>(tiles < cap ? tiles : cap), 128 * S, smem, stream>>>(
-        s, p, maps, x_map, static_cast<T *>(y), y_stride, rows, rows_vector_ok(y, y_stride, s.d_out));
+        s, p, maps, x_map, static_cast<T *>(y), y_stride, rows, y ? rows_vector_ok(y, y_stride, s.d_out) : 0, mse);
     return launch_status("mlp_fwd_pipe_kernel launch");
+}
+
+// Four slots measured best (2^21 rows, 32-64-64-16: 3 slots 0.136 ms, 4: 0.103, 5: 0.116, 6: 0.126; the
+// one-tile-per-CTA kernel: 0.193): MMA operand reads and epilogue stores share the SM's shared-memory
+// bandwidth, and beyond four tiles in flight they only queue up behind each other.  Fewer are used
+// (three) when the weights leave less room; TH_MLP_SLOTS=3 or 0 lowers the cap (0 = never).
+template <typename T, int ACT, bool BIAS, bool MSE>
+int launch_fwd_slots(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, void *y, int64_t y_stride,
+                     int64_t rows, cudaStream_t stream, const MseArgs &mse) {
+    static const int cap = [] {
+        const char *v = getenv("TH_MLP_SLOTS");
+        return v ? atoi(v) : 4;
+    }();
+    int rc = kTcNotApplicable;
+    if (cap >= 4) rc = launch_fwd_pipe<T, ACT, BIAS, 4, MSE>(s, p, x, x_stride, y, y_stride, rows, stream, mse);
+    if (rc == kTcNotApplicable && cap >= 3) rc = launch_fwd_pipe<T, ACT, BIAS, 3, MSE>(s, p, x, x_stride, y, y_stride, rows, stream, mse);
+    return rc;
 }
 
 template <typename T, int ACT, bool BIAS>
 int launch_fwd_t(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, void *y, int64_t y_stride,
                  int64_t rows, cudaStream_t stream) {
     {
-        // Four slots measured best (2^21 rows, 32-64-64-16: 3 slots 0.136 ms, 4: 0.103, 5: 0.116, 6: 0.126;
-        // the kernel above: 0.193): MMA operand reads and epilogue stores share the SM's shared-memory
-        // bandwidth, and beyond four tiles in flight they only queue up behind each other.  Fewer are
-        // used when the weights leave less room; TH_MLP_SLOTS overrides the cap (0 = never).
-        static const int cap = [] {
-            const char *v = getenv("TH_MLP_SLOTS");
-            return v ? atoi(v) : 4;
-        }();
-        int rc = kTcNotApplicable;
-        if (cap >= 6) rc = launch_fwd_pipe<T, ACT, BIAS, 6>(s, p, x, x_stride, y, y_stride, rows, stream);
-        if (rc == kTcNotApplicable && cap >= 5) rc = launch_fwd_pipe<T, ACT, BIAS, 5>(s, p, x, x_stride, y, y_stride, rows, stream);
-        if (rc == kTcNotApplicable && cap >= 4) rc = launch_fwd_pipe<T, ACT, BIAS, 4>(s, p, x, x_stride, y, y_stride, rows, stream);
-        if (rc == kTcNotApplicable && cap >= 3) rc = launch_fwd_pipe<T, ACT, BIAS, 3>(s, p, x, x_stride, y, y_stride, rows, stream);
+        const int rc = launch_fwd_slots<T, ACT, BIAS, false>(s, p, x, x_stride, y, y_stride, rows, stream, MseArgs{});
         if (rc != kTcNotApplicable) return rc;
     }
     const TcPlan P = tc_plan(s, false);
@@ -1259,7 +1297,42 @@ int launch_bwd(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_s
                : launch_bwd_t<T, TH_ACT_NONE>(s, p, x, x_stride, go, go_stride, gx, gx_stride, workspace, rows, stream);
 }
 
+// ---- forward with the fused MSE epilogue: only the multi-slot kernel has it ----
+
+template <typename T, bool BIAS>
+int launch_fwd_mse_act(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, void *y, int64_t y_stride,
+                       const MseArgs &mse, int64_t rows, cudaStream_t stream) {
+    switch (s.act) {
+        case TH_ACT_RELU: return launch_fwd_slots<T, TH_ACT_RELU, BIAS, true>(s, p, x, x_stride, y, y_stride, rows, stream, mse);
+        case TH_ACT_SILU: return launch_fwd_slots<T, TH_ACT_SILU, BIAS, true>(s, p, x, x_stride, y, y_stride, rows, stream, mse);
+        case TH_ACT_RELU2: return launch_fwd_slots<T, TH_ACT_RELU2, BIAS, true>(s, p, x, x_stride, y, y_stride, rows, stream, mse);
+        default: return launch_fwd_slots<T, TH_ACT_NONE, BIAS, true>(s, p, x, x_stride, y, y_stride, rows, stream, mse);
+    }
+}
+
+template <typename T>
+int launch_fwd_mse(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, void *y, int64_t y_stride,
+                   const MseArgs &mse, int64_t rows, cudaStream_t stream) {
+    return s.has_bias ? launch_fwd_mse_act<T, true>(s, p, x, x_stride, y, y_stride, mse, rows, stream)
+                      : launch_fwd_mse_act<T, false>(s, p, x, x_stride, y, y_stride, mse, rows, stream);
+}
+
 }  // namespace
+
+int mlp_fwd_mse_tc(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, void *y, int64_t y_stride,
+                   const MseArgs &mse, int64_t rows, int dtype, cudaStream_t stream) {
+    if (tc_disabled() || rows <= 0) return kTcNotApplicable;
+    if (s.h != 16 && s.h != 32 && s.h != 64) return kTcNotApplicable;
+    // whole 16-byte chunks of every row: prediction (if kept), target and gradient
+    if (s.d_out % 8 != 0 || !rows_vector_ok(mse.target, mse.target_stride, s.d_out) ||
+        !rows_vector_ok(mse.grad, mse.grad_stride, s.d_out) || (y && !rows_vector_ok(y, y_stride, s.d_out)))
+        return kTcNotApplicable;
+    switch (dtype) {
+        case TH_F16: return launch_fwd_mse<__half>(s, p, x, x_stride, y, y_stride, mse, rows, stream);
+        case TH_BF16: return launch_fwd_mse<__nv_bfloat16>(s, p, x, x_stride, y, y_stride, mse, rows, stream);
+        default: return kTcNotApplicable;
+    }
+}
 
 int mlp_fwd_tc(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, void *y, int64_t y_stride,
                int64_t rows, int dtype, cudaStream_t stream) {

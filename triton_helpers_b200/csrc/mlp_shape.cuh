@@ -52,6 +52,21 @@ constexpr int kTcNotApplicable = -1000;
 int mlp_fwd_tc(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, void *y, int64_t y_stride,
                int64_t rows, int dtype, cudaStream_t stream);
 
+// Forward with the squared-error loss fused into the output epilogue: instead of (or besides, when
+// `y` is given) the prediction, each output row leaves as grad = (prediction - target) * grad_scale,
+// and sum (prediction - target)^2 is added to *loss_sum.  The prediction is rounded to the 16-bit
+// dtype first, so the values equal those of the unfused sequence (forward, then the MSE kernel).
+struct MseArgs {
+    const void *target;
+    long long target_stride;
+    void *grad;
+    long long grad_stride;
+    float *loss_sum;
+    float grad_scale;
+};
+int mlp_fwd_mse_tc(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, void *y, int64_t y_stride,
+                   const MseArgs &mse, int64_t rows, int dtype, cudaStream_t stream);
+
 // Accumulates the parameter gradients into `workspace` (fp32, already zeroed, laid out by
 // grad_workspace_layout) and writes grad_x; the caller rounds the workspace into the gradient tensors.
 int mlp_bwd_tc(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, const void *go,

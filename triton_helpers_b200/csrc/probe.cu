@@ -67,7 +67,7 @@ __global__ void __launch_bounds__(kProbeThreads) l2_update_kernel(unsigned *__re
 }  // namespace
 }  // namespace th
 
-extern "C" int th_probe_l2(const void *buffer, int64_t n_bytes, int mode, int iters, void *sink, int64_t *work_out,
+extern "C" int th_probe_l2(void *buffer, int64_t n_bytes, int mode, int iters, void *sink, int64_t *work_out,
                            void *stream) {
     using namespace th;
     if (!buffer || !sink || n_bytes < 4096 || iters < 1) return fail(TH_ERR_BAD_ARG, "th_probe_l2: buffer, sink, n_bytes >= 4096 and iters >= 1 are required");
@@ -85,7 +85,7 @@ extern "C" int th_probe_l2(const void *buffer, int64_t n_bytes, int mode, int it
             l2_gather_kernel<<<ctas, kProbeThreads, 0, s>>>(static_cast<const unsigned *>(buffer), static_cast<unsigned>(n_bytes / 32),
                                                             iters, static_cast<unsigned *>(sink));
         else
-            l2_update_kernel<<<ctas, kProbeThreads, 0, s>>>(static_cast<unsigned *>(const_cast<void *>(buffer)),
+            l2_update_kernel<<<ctas, kProbeThreads, 0, s>>>(static_cast<unsigned *>(buffer),
                                                             static_cast<unsigned>(n_bytes / 32), iters);
         if (work_out) *work_out = static_cast<int64_t>(ctas) * kProbeThreads * 8 * iters;
     }

@@ -109,22 +109,21 @@ __device__ __forceinline__ void tile_row_to_tmem(unsigned char *tile, const Seat
 template <typename T, bool BIAS>
 __device__ __forceinline__ void stream_epilogue(uint32_t taddr, const Seat &seat, int width, const float *bias,
                                                 unsigned char *tile, T *global_row, bool live) {
-    const int count = width / (8 * kGroups), first = seat.group * count;
-    uint32_t raw[kMaxChunks][8];
-    load_pieces(taddr, first, count, raw);
+    const int n = width / kGroups, first = seat.group * (n / 8);  // this thread's columns / first 8-column piece
+    const uint32_t row_addr = (tile ? smem_addr(tile) : 0u) + seat.row * 128, row_swizzle = (seat.row & 7) << 4;
+    for_each_piece(taddr + seat.group * n, n, [&](int u, const uint32_t(&piece)[8]) {
+        uint32_t v[8];
 #pragma unroll
-    for (int u = 0; u < kMaxChunks; ++u) {
-        if (u < count) {
-            if constexpr (BIAS) {
+        for (int k = 0; k < 8; ++k) v[k] = piece[k];
+        if constexpr (BIAS) {
 #pragma unroll
-                for (int k = 0; k < 8; ++k) raw[u][k] = __float_as_uint(__uint_as_float(raw[u][k]) + bias[8 * (first + u) + k]);
-                tmem_st8(taddr + 8 * (first + u), raw[u]);
-            }
-            const uint4 packed = finish_piece<T, TH_ACT_NONE, false>(raw[u], nullptr);
-            if (tile) *reinterpret_cast<uint4 *>(chunk_ptr(tile, seat.row, first + u)) = packed;
-            if (global_row && live) __stcs(reinterpret_cast<uint4 *>(global_row + 8 * (first + u)), packed);
+            for (int k = 0; k < 8; ++k) v[k] = __float_as_uint(__uint_as_float(v[k]) + bias[8 * (first + u) + k]);
+            tmem_st8(taddr + 8 * (first + u), v);
         }
-    }
+        const uint4 packed = finish8<T, TH_ACT_NONE, false>(v, nullptr);
+        if (tile) st_shared_16(row_addr + (((first + u) << 4) ^ row_swizzle), packed);
+        if (global_row && live) __stcs(reinterpret_cast<uint4 *>(global_row + 8 * (first + u)), packed);
+    });
     if constexpr (BIAS) tmem_st_wait();
 }
 
@@ -202,14 +201,12 @@ rev_fwd_tc_kernel(const RevShape s, const RevParams p, const T *__restrict__ x, 
                 }
                 commit_and_wait(leader, bar, phase, &abort_flag);
                 {
-                    const int count = s.hid / (8 * kGroups), first = seat.group * count;
-                    uint32_t raw[kMaxChunks][8];
-                    load_pieces(taddr + kFwdHid, first, count, raw);
-#pragma unroll
-                    for (int u = 0; u < kMaxChunks; ++u)
-                        if (u < count)
-                            *reinterpret_cast<uint4 *>(chunk_ptr(h_tile, seat.row, first + u)) =
-                                finish_piece<T, ACT, BIAS>(raw[u], bias + (2 * branch) * kMaxDim + 8 * (first + u));
+                    const int n = s.hid / kGroups, first = seat.group * (n / 8);
+                    const uint32_t row_addr = smem_addr(h_tile) + seat.row * 128, row_swizzle = (seat.row & 7) << 4;
+                    const float *layer_bias = bias + (2 * branch) * kMaxDim;
+                    for_each_piece(taddr + kFwdHid + seat.group * n, n, [&](int u, const uint32_t(&piece)[8]) {
+                        st_shared_16(row_addr + (((first + u) << 4) ^ row_swizzle), finish8<T, ACT, BIAS>(piece, layer_bias + 8 * (first + u)));
+                    });
                 }
                 publish_tiles();
                 if (threadIdx.x < 32) {
@@ -329,25 +326,25 @@ rev_bwd_tc_kernel(const RevShape s, const RevParams p, const T *__restrict__ y, 
                 }
                 commit_and_wait(leader, bar, phase, &abort_flag);
                 {
-                    const int count = s.hid / (8 * kGroups), first = seat.group * count;
-                    uint32_t zraw[kMaxChunks][8], draw[kMaxChunks][8];
-                    load_pieces(taddr + kZ, first, count, zraw);
-                    load_pieces(taddr + kDH, first, count, draw);
-#pragma unroll
-                    for (int u = 0; u < kMaxChunks; ++u) {
-                        if (u < count) {
-                            const uint4 h = finish_piece<T, ACT, false>(zraw[u], nullptr);
-                            uint4 g = finish_piece<T, TH_ACT_NONE, false>(draw[u], nullptr);
-                            if constexpr (ACT == TH_ACT_RELU) {
-                                g.x = keep_where_positive<T>(g.x, h.x);
-                                g.y = keep_where_positive<T>(g.y, h.y);
-                                g.z = keep_where_positive<T>(g.z, h.z);
-                                g.w = keep_where_positive<T>(g.w, h.w);
-                            }
-                            *reinterpret_cast<uint4 *>(chunk_ptr(h_tile, seat.row, first + u)) = h;
-                            *reinterpret_cast<uint4 *>(chunk_ptr(dz_tile, seat.row, first + u)) = g;
+                    // h = act(z) first (also the ReLU mask), then dz = dh where h > 0
+                    const int n = s.hid / kGroups, first = seat.group * (n / 8);
+                    const uint32_t row_off = seat.row * 128, row_swizzle = (seat.row & 7) << 4;
+                    const uint32_t h_row = smem_addr(h_tile) + row_off, dz_row = smem_addr(dz_tile) + row_off;
+                    for_each_piece(taddr + kZ + seat.group * n, n, [&](int u, const uint32_t(&piece)[8]) {
+                        st_shared_16(h_row + (((first + u) << 4) ^ row_swizzle), finish8<T, ACT, false>(piece, nullptr));
+                    });
+                    for_each_piece(taddr + kDH + seat.group * n, n, [&](int u, const uint32_t(&piece)[8]) {
+                        const uint32_t off = ((first + u) << 4) ^ row_swizzle;
+                        uint4 g = finish8<T, TH_ACT_NONE, false>(piece, nullptr);
+                        if constexpr (ACT == TH_ACT_RELU) {
+                            const uint4 h = ld_shared_16(h_row + off);  // this thread's own store above
+                            g.x = keep_where_positive<T>(g.x, h.x);
+                            g.y = keep_where_positive<T>(g.y, h.y);
+                            g.z = keep_where_positive<T>(g.z, h.z);
+                            g.w = keep_where_positive<T>(g.w, h.w);
                         }
-                    }
+                        st_shared_16(dz_row + off, g);
+                    });
                 }
                 publish_tiles();
                 // step B: undo the branch, push the gradient through, form both weight gradients

@@ -273,20 +273,27 @@ __device__ __forceinline__ uint4 ld_shared_16(uint32_t addr) {
     return v;
 }
 
-// N (8, 16 or 32) consecutive accumulator columns of this thread's lane, then `fn(u, eight values)`
+// N (8, 16, 24 or 32) consecutive accumulator columns of this thread's lane, then `fn(u, eight values)`
 // for each 8-column piece u; everything is sized at compile time so the values stay in registers.
+__device__ __forceinline__ void tmem_ld8_at(uint32_t taddr, uint32_t *r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+
 template <int N, typename Fn>
 __device__ __forceinline__ void for_each_piece_n(uint32_t taddr, Fn fn) {
     uint32_t raw[32];
     if constexpr (N == 32) {
         tmem_ld32(taddr, raw);
+    } else if constexpr (N == 24) {
+        tmem_ld16(taddr, raw);
+        tmem_ld8_at(taddr + 16, raw + 16);
     } else if constexpr (N == 16) {
         tmem_ld16(taddr, raw);
     } else {
-        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                     : "=r"(raw[0]), "=r"(raw[1]), "=r"(raw[2]), "=r"(raw[3]), "=r"(raw[4]), "=r"(raw[5]), "=r"(raw[6]), "=r"(raw[7])
-                     : "r"(taddr)
-                     : "memory");
+        tmem_ld8_at(taddr, raw);
     }
     tmem_ld_wait();
 #pragma unroll
@@ -296,10 +303,12 @@ __device__ __forceinline__ void for_each_piece_n(uint32_t taddr, Fn fn) {
         fn(u, piece);
     }
 }
-// the same for a run-time n in {8, 16, 32} (warp uniform)
+// the same for a run-time n in {8, 16, 24, 32} (warp uniform; padded widths are multiples of 16 and
+// two threads share a row)
 template <typename Fn>
 __device__ __forceinline__ void for_each_piece(uint32_t taddr, int n, Fn fn) {
     if (n == 32) for_each_piece_n<32>(taddr, fn);
+    else if (n == 24) for_each_piece_n<24>(taddr, fn);
     else if (n == 16) for_each_piece_n<16>(taddr, fn);
     else for_each_piece_n<8>(taddr, fn);
 }

@@ -190,3 +190,109 @@ def fully_fused_mlp(
     """
     activation = ensure_str(activation)
     return _fully_fused_mlp.apply(x, w_in, b_in, w_out, b_out, w_hid, b_hid, activation, fp16_acc)
+
+
+class _fully_fused_mlp_mse(torch.autograd.Function):
+    r"""Forward pass and squared-error loss in one kernel; see ``fully_fused_mlp_mse``."""
+
+    @staticmethod
+    def forward(ctx, x, w_in, w_out, w_hid, target, grad_scale, activation):
+        B, L, D_in = x.shape
+        D_hidden, D_out = w_in.shape[0], w_out.shape[0]
+        depth = 1 if w_hid is None else w_hid.shape[0] // D_hidden + 1
+        device = _lib.require_cuda(x, w_in, w_out, w_hid, target)
+        dtype = x.dtype
+        assert dtype in (torch.float16, torch.bfloat16) and all(
+            t is None or t.dtype == dtype for t in (w_in, w_out, w_hid, target)
+        ), "fused forward + MSE takes float16 or bfloat16 tensors of one dtype"
+        assert target.shape == (B, L, D_out), "target shape mismatch"
+        x, target = _rows_view(x), _rows_view(target)
+        w_in, w_out = w_in.contiguous(), w_out.contiguous()
+        w_hid = None if w_hid is None else w_hid.contiguous()
+        grad = x.new_empty((B, L, D_out))
+        loss_sum = torch.zeros(1, dtype=torch.float32, device=device)
+        lib = _lib.lib()
+        with torch.cuda.device(device):
+            code = lib.th_mlp_fwd_mse(
+                x.data_ptr(), x.stride(1), w_in.data_ptr(), None, _lib.ptr(w_hid), None, w_out.data_ptr(), None,
+                None, D_out, target.data_ptr(), target.stride(1), grad.data_ptr(), D_out, loss_sum.data_ptr(),
+                grad_scale, B * L, D_in, D_hidden, D_out, depth, _lib.ACTIVATION_CODE[activation],
+                _lib.DTYPE_CODE[dtype], _lib.stream_ptr(device),
+            )  # fmt: skip
+            if code == _lib.TH_ERR_UNSUPPORTED:
+                # shapes the fused kernel does not take: the two kernels it stands for
+                o = x.new_empty((B, L, D_out))
+                _lib.check(
+                    lib.th_mlp_fwd(
+                        x.data_ptr(), x.stride(1), w_in.data_ptr(), None, _lib.ptr(w_hid), None, w_out.data_ptr(), None,
+                        o.data_ptr(), D_out, B * L, D_in, D_hidden, D_out, depth, _lib.ACTIVATION_CODE[activation],
+                        _lib.DTYPE_CODE[dtype], 0, _lib.stream_ptr(device),
+                    ),
+                    "th_mlp_fwd",
+                )  # fmt: skip
+                target_c = target.contiguous()
+                _lib.check(
+                    lib.th_mse_grad(
+                        o.data_ptr(), target_c.data_ptr(), grad.data_ptr(), loss_sum.data_ptr(), o.numel(), grad_scale,
+                        _lib.DTYPE_CODE[dtype], _lib.stream_ptr(device),
+                    ),
+                    "th_mse_grad",
+                )  # fmt: skip
+            else:
+                _lib.check(code, "th_mlp_fwd_mse")
+        ctx.save_for_backward(x, w_in, w_out, w_hid, grad)
+        ctx.activation, ctx.depth = activation, depth
+        return loss_sum
+
+    @staticmethod
+    @torch.no_grad()
+    def backward(ctx, d_loss: Tensor):
+        # The gradients of (grad_scale / 2) * loss_sum; the incoming gradient is taken to be one.
+        x, w_in, w_out, w_hid, grad = ctx.saved_tensors
+        B, L, D_in = x.shape
+        D_hidden, D_out = w_in.shape[0], w_out.shape[0]
+        device, dtype = x.device, x.dtype
+        dx = x.new_empty((B, L, D_in)) if ctx.needs_input_grad[0] else None
+        dw_in, dw_out = torch.empty_like(w_in), torch.empty_like(w_out)
+        dw_hid = None if w_hid is None else torch.empty_like(w_hid)
+        ws_bytes = _lib.lib().th_mlp_workspace_bytes(D_in, D_hidden, D_out, ctx.depth)
+        workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=device)
+        with torch.cuda.device(device):
+            _lib.check(
+                _lib.lib().th_mlp_bwd(
+                    x.data_ptr(), x.stride(1), w_in.data_ptr(), None, _lib.ptr(w_hid), None, w_out.data_ptr(), None,
+                    grad.data_ptr(), D_out, _lib.ptr(dx), D_in, dw_in.data_ptr(), None, _lib.ptr(dw_hid), None,
+                    dw_out.data_ptr(), None, workspace.data_ptr(), ws_bytes, B * L, D_in, D_hidden, D_out, ctx.depth,
+                    _lib.ACTIVATION_CODE[ctx.activation], _lib.DTYPE_CODE[dtype], 0, _lib.stream_ptr(device),
+                ),
+                "th_mlp_bwd",
+            )  # fmt: skip
+        return dx, dw_in, dw_out, dw_hid, None, None, None
+
+
+def fully_fused_mlp_mse(
+    x: Tensor,
+    w_in: Tensor,
+    w_out: Tensor,
+    w_hid: Optional[Tensor],
+    target: Tensor,
+    grad_scale: float = 1.0,
+    activation: str = "relu",
+) -> Tensor:
+    r"""Bias-free MLP forward with the squared-error loss fused into its output layer.
+
+    Returns ``loss_sum = sum((mlp(x) - target) ** 2)`` as a one-element float32 tensor; the prediction
+    is never written to memory.  What the kernel does write is ``(mlp(x) - target) * grad_scale`` in
+    the 16-bit dtype, and ``loss_sum.backward()`` back-propagates exactly that tensor: the gradients
+    it leaves are those of ``grad_scale / 2 * loss_sum`` (a training loop folds the factor into its
+    optimiser step, as ``training.NeuralFieldTrainer`` does, so that 16-bit gradients neither
+    underflow nor overflow).  The incoming gradient of ``loss_sum`` is taken to be one.
+    triton_helpers has no such function; it is the fusion of ``fully_fused_mlp`` with the loss
+    that follows it in a regression loop.
+
+    Shapes:
+        - x: :math:`(B, L, D_{in})`, target: :math:`(B, L, D_{out})`, weights as in ``fully_fused_mlp``.
+    """
+    activation = ensure_str(activation)
+    assert activation in ACTIVATIONS, f"Invalid activation function: {activation}"
+    return _fully_fused_mlp_mse.apply(x, w_in, w_out, w_hid, target, float(grad_scale), activation)

@@ -16,7 +16,7 @@ import torch.nn as nn
 from torch import Tensor
 
 from . import _lib
-from .layers.fully_fused_mlp import FullyFusedMLP
+from .layers.fully_fused_mlp import FullyFusedMLP, fully_fused_mlp_mse
 from .layers.hash_encoding import HashEncoding
 from .layers.hash_encoding.helpers import level_geometry
 from .layers.hash_encoding.kernel import hash_encoding_backward_levels
@@ -97,24 +97,43 @@ class NeuralFieldTrainer(nn.Module):
         world = self.world_size()
         passes = self.backward_passes
         if passes is None:
-            pred, loss_sum = self._backward_through_autograd(coords, targets)
+            n_values, loss_sum = self._backward_through_autograd(coords, targets)
         else:
-            pred, loss_sum = self._backward_in_level_passes(coords, targets, passes)
+            n_values, loss_sum = self._backward_in_level_passes(coords, targets, passes)
         # d(mean over the global batch)/d pred = 2 (pred - target) / (N_global * C)
-        true_over_stored = 2.0 / (pred.numel() * world * self.grad_out_scale)
+        true_over_stored = 2.0 / (n_values * world * self.grad_out_scale)
         self.optimizer.step(grad_scale=true_over_stored)
         for p in self.parameters():
             p.grad = None
-        return loss_sum / pred.numel()
+        return loss_sum / n_values
 
-    def _backward_through_autograd(self, coords: Tensor, targets: Tensor) -> Tuple[Tensor, Tensor]:
-        pred = self.forward(coords)
+    def _fusable(self) -> bool:
+        r"""Whether the MLP's last layer and the loss can share a kernel (bias-free 16-bit network)."""
+        mlp = self.mlp
+        return mlp.b_in is None and mlp.w_in.dtype in (torch.float16, torch.bfloat16)
+
+    def _loss_backward(self, feats: Tensor, targets: Tensor) -> Tuple[int, Tensor]:
+        r"""MLP forward, squared error and the whole backward below ``feats``' producer.  Returns the
+        number of predicted values and the float32 sum of squared errors."""
+        mlp = self.mlp
+        if self._fusable():
+            loss_sum = fully_fused_mlp_mse(
+                feats.unsqueeze(0), mlp.w_in, mlp.w_out, mlp.w_hid, targets.to(feats.dtype).unsqueeze(0),
+                self.grad_out_scale, mlp.activation,
+            )  # fmt: skip
+            loss_sum.backward()
+            return targets.numel(), loss_sum.detach()
+        pred = mlp(feats.unsqueeze(0)).squeeze(0)
         grad_out, loss_sum = mse_grad(pred, targets.to(pred.dtype), self.grad_out_scale)
         pred.backward(grad_out)
-        allreduce_gradients([p.grad for p in self.parameters() if p.grad is not None], self.group)
-        return pred, loss_sum
+        return pred.numel(), loss_sum
 
-    def _backward_in_level_passes(self, coords: Tensor, targets: Tensor, n_passes: int) -> Tuple[Tensor, Tensor]:
+    def _backward_through_autograd(self, coords: Tensor, targets: Tensor) -> Tuple[int, Tensor]:
+        n_values, loss_sum = self._loss_backward(self.encoding(coords), targets)
+        allreduce_gradients([p.grad for p in self.parameters() if p.grad is not None], self.group)
+        return n_values, loss_sum
+
+    def _backward_in_level_passes(self, coords: Tensor, targets: Tensor, n_passes: int) -> Tuple[int, Tensor]:
         r"""The same gradients with the exchange overlapped: autograd covers the MLP only; the encoding
         backward is launched range by range (finest levels first) and each finished range of table
         rows goes to an asynchronous all-reduce while the next range is computed."""
@@ -122,9 +141,7 @@ class NeuralFieldTrainer(nn.Module):
         with torch.no_grad():
             feats = enc(coords)
         feats.requires_grad_(True)
-        pred = self.mlp(feats.unsqueeze(0)).squeeze(0)
-        grad_out, loss_sum = mse_grad(pred, targets.to(pred.dtype), self.grad_out_scale)
-        pred.backward(grad_out)
+        n_values, loss_sum = self._loss_backward(feats, targets)
         pending = PendingReduce(self.group)
         pending.start([p.grad for p in self.mlp.parameters() if p.grad is not None])
         table = enc.embeddings
@@ -140,4 +157,4 @@ class NeuralFieldTrainer(nn.Module):
             pending.start([grad_table[first_row:last_row]])
         pending.finish()
         table.grad = grad_table
-        return pred, loss_sum
+        return n_values, loss_sum
