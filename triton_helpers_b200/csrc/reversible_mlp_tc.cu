@@ -232,26 +232,22 @@ rev_fwd_tc_kernel(const RevShape s, const RevParams p, const T *__restrict__ x, 
 
 // One weight-gradient accumulator (M = 64 layout) out of TMEM, added into this CTA's private copy.
 __device__ __forceinline__ void flush_dw_private(uint32_t taddr, const Seat &seat, int out_dim, int in_dim, float *dst) {
-    const int count = in_dim / (8 * kGroups), first = seat.group * count;
-    uint32_t raw[kMaxChunks][8];
-    load_pieces(taddr, first, count, raw);
+    const int n = in_dim / kGroups, first = seat.group * (n / 8);  // this thread's columns / first 8-column piece
     const int lane = threadIdx.x & 31;
     const int m = 16 * ((threadIdx.x >> 5) & 3) + lane;
-    if (lane < 16 && m < out_dim) {
-        // fire-and-forget vector reductions: no round trip to wait for, and nobody else touches this copy
+    const bool owner = lane < 16 && m < out_dim;
+    // fire-and-forget vector reductions: no round trip to wait for, and nobody else touches this copy
+    for_each_piece(taddr + seat.group * n, n, [&](int u, const uint32_t(&piece)[8]) {
+        if (owner) {
+            float *q = dst + m * 64 + 8 * (first + u);
 #pragma unroll
-        for (int u = 0; u < kMaxChunks; ++u) {
-            if (u < count) {
-                float *q = dst + m * 64 + 8 * (first + u);
-#pragma unroll
-                for (int h = 0; h < 2; ++h)
-                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(q + 4 * h),
-                                 "f"(__uint_as_float(raw[u][4 * h])), "f"(__uint_as_float(raw[u][4 * h + 1])),
-                                 "f"(__uint_as_float(raw[u][4 * h + 2])), "f"(__uint_as_float(raw[u][4 * h + 3]))
-                                 : "memory");
-            }
+            for (int h = 0; h < 2; ++h)
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(q + 4 * h),
+                             "f"(__uint_as_float(piece[4 * h])), "f"(__uint_as_float(piece[4 * h + 1])),
+                             "f"(__uint_as_float(piece[4 * h + 2])), "f"(__uint_as_float(piece[4 * h + 3]))
+                             : "memory");
         }
-    }
+    });
 }
 
 template <typename T, int ACT>
