@@ -41,11 +41,8 @@
 #include "mlp_shape.cuh"
 #include "tc_tiles.cuh"
 
-#include <cuda.h>  // CUtensorMap and its enums only; the driver entry point is looked up at run time
-
 #include <cstdlib>
 #include <cstring>
-#include <mutex>
 #include <type_traits>
 
 namespace th {
@@ -100,14 +97,6 @@ __device__ __forceinline__ unsigned char *weight_tile(unsigned char *smem, const
 struct WeightMaps {
     CUtensorMap w_in, w_hid, w_out;
 };
-
-__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint32_t mbar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-            smem_addr(smem_dst)),
-        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(mbar)
-        : "memory");
-}
 
 // All weight tiles of the network by TMA: thread 0 arms the barrier with the byte count and issues
 // one box per layer; everybody waits (bounded) for the bytes to land.  Returns false on a timeout.
@@ -1081,41 +1070,6 @@ int occupancy_plan(const TcPlan &P, int *ctas_per_sm) {
 }
 
 // ---- tensor maps for the weights ---------------------------------------------------------------
-
-using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-// cuTensorMapEncodeTiled through the runtime's driver-entry-point lookup (no link against libcuda).
-EncodeTiledFn encode_tiled_fn() {
-    static std::mutex guard;
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    std::lock_guard<std::mutex> lock(guard);
-    if (!tried) {
-        tried = true;
-        void *ptr = nullptr;
-        cudaDriverEntryPointQueryResult status;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &status) == cudaSuccess &&
-            status == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
-    return fn;
-}
-
-// One map per weight array: [rows][cols] 16-bit row-major, box = 64 columns x box_rows rows.
-bool make_map(CUtensorMap *map, const void *base, long long rows, int cols, int box_rows, long long row_stride = 0) {
-    EncodeTiledFn encode = encode_tiled_fn();
-    if (row_stride == 0) row_stride = cols;
-    if (!encode || !base || cols % 8 != 0 || row_stride % 8 != 0 || !aligned_to(base, 16)) return false;
-    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_stride) * 2};
-    const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
-    const cuuint32_t elem[2] = {1, 1};
-    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void *>(base), dims, strides, box, elem,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
 
 // Returns 1 when all three maps could be built (then the kernels load the weights by TMA), else 0.
 int make_weight_maps(WeightMaps &maps, const MlpShape &s, const MlpParams &p) {

@@ -28,6 +28,7 @@
 #include "tc_tiles.cuh"
 
 #include <cstdlib>
+#include <cstring>
 #include <type_traits>
 
 namespace th {
@@ -90,6 +91,44 @@ __device__ void prefetch_weights(unsigned char *smem, const RevTcPlan &P, const 
     asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
+// The same by TMA: one 64-column box per matrix lands in the operand-tile layout, issued by one thread
+// and counted on the ring stage's mbarrier (the cp.async version above keeps every thread busy for
+// ~1 800 cycles per block).  Biases, when present, still come with plain loads.
+struct RevWeightMaps {
+    CUtensorMap m[4];  // w_f1, w_f2, w_g1, w_g2: [blocks * rows][cols], 16-bit
+};
+
+template <typename T>
+__device__ void prefetch_weights_tma(unsigned char *smem, const RevTcPlan &P, const RevShape &s, const RevParams &p,
+                                     const RevWeightMaps &maps, unsigned long long *ring_bars, int k, int stage) {
+    if (threadIdx.x == 64) {  // not warp 0, which is about to issue MMAs
+        const uint32_t bar = smem_addr(&ring_bars[stage]);
+        const uint32_t bytes = static_cast<uint32_t>(2 * (s.hid + s.half) * 128);  // four boxes of 64 columns
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            const int rows = (m & 1) ? s.half : s.hid;
+            tma_load_2d(smem + P.ring + stage * kStageBytes + m * kWTileBytes, &maps.m[m], 0, k * rows, bar);
+        }
+    }
+    if (s.has_bias) {
+        float *bias = reinterpret_cast<float *>(smem + P.bias) + stage * 4 * kMaxDim;
+        const T *bsrc[4] = {static_cast<const T *>(p.b_f1), static_cast<const T *>(p.b_f2), static_cast<const T *>(p.b_g1),
+                            static_cast<const T *>(p.b_g2)};
+        for (int e = threadIdx.x; e < 4 * kMaxDim; e += kTcThreads) {
+            const int m = e / kMaxDim, c = e % kMaxDim;
+            const int width = (m & 1) ? s.half : s.hid;
+            bias[e] = c < width ? to_float<T>(bsrc[m][k * width + c]) : 0.f;
+        }
+    }
+}
+
+// Warp 0 waits (bounded) for the ring stage used by running step `step`; the CTA barrier that follows
+// in the caller hands the result to everybody.
+__device__ __forceinline__ void ring_wait(unsigned long long *ring_bars, int step, int *abort_flag) {
+    if (threadIdx.x < 32 && !mbar_wait(smem_addr(&ring_bars[step & 1]), static_cast<uint32_t>((step >> 1) & 1))) *abort_flag = 1;
+}
+
 // This thread's pieces of a 16-bit operand tile row -> fp32 in TMEM (stream initialisation)
 template <typename T>
 __device__ __forceinline__ void tile_row_to_tmem(unsigned char *tile, const Seat &seat, int width, uint32_t taddr) {
@@ -145,8 +184,8 @@ __device__ __forceinline__ void publish_tiles() {
 
 template <typename T, int ACT, bool BIAS>
 __global__ void __launch_bounds__(kTcThreads, 2)
-rev_fwd_tc_kernel(const RevShape s, const RevParams p, const T *__restrict__ x, long long x_stride, T *__restrict__ y,
-                  long long y_stride, long long n_rows) {
+rev_fwd_tc_kernel(const RevShape s, const RevParams p, const __grid_constant__ RevWeightMaps maps, const int use_tma,
+                  const T *__restrict__ x, long long x_stride, T *__restrict__ y, long long y_stride, long long n_rows) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint32_t tmem_holder;
@@ -156,10 +195,19 @@ rev_fwd_tc_kernel(const RevShape s, const RevParams p, const T *__restrict__ x, 
     constexpr int bf16 = std::is_same<T, __half>::value ? 0 : 1;
     unsigned char *u_tile = smem, *h_tile = smem + kTileBytes;
 
-    if (threadIdx.x == 0) abort_flag = 0;
+    __shared__ __align__(8) unsigned long long ring_bars[2];
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&ring_bars[0])), "r"(1u) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&ring_bars[1])), "r"(1u) : "memory");
+    }
     const long long n_tiles = (n_rows + kTileRows - 1) / kTileRows;
-    if (static_cast<long long>(blockIdx.x) < n_tiles) prefetch_weights<T>(smem, P, s, p, 0, 0);
-    const uint32_t tmem = cta_setup(&tmem_holder, &mbar, P.tmem_cols);
+    if (!use_tma && static_cast<long long>(blockIdx.x) < n_tiles) prefetch_weights<T>(smem, P, s, p, 0, 0);
+    const uint32_t tmem = cta_setup(&tmem_holder, &mbar, P.tmem_cols);  // publishes the barrier inits
+    if (use_tma && static_cast<long long>(blockIdx.x) < n_tiles) {
+        prefetch_weights_tma<T>(smem, P, s, p, maps, ring_bars, 0, 0);
+        ring_wait(ring_bars, 0, &abort_flag);
+    }
     const uint32_t bar = smem_addr(&mbar);
     const Seat seat;
     const uint32_t taddr = tmem + seat.lane_base;
@@ -184,8 +232,11 @@ rev_fwd_tc_kernel(const RevShape s, const RevParams p, const T *__restrict__ x, 
         for (int k = 0; k < s.blocks && !abort_flag; ++k, ++step) {
             const int stage = step & 1;
             // the other stage was last read by the previous block, whose GEMMs have all completed
-            if (k + 1 < s.blocks || tile + gridDim.x < n_tiles)
-                prefetch_weights<T>(smem, P, s, p, (k + 1) % s.blocks, stage ^ 1);
+            const bool more = k + 1 < s.blocks || tile + gridDim.x < n_tiles;
+            if (more) {
+                if (use_tma) prefetch_weights_tma<T>(smem, P, s, p, maps, ring_bars, (k + 1) % s.blocks, stage ^ 1);
+                else prefetch_weights<T>(smem, P, s, p, (k + 1) % s.blocks, stage ^ 1);
+            }
             const unsigned char *w = smem + P.ring + stage * kStageBytes;
             const float *bias = reinterpret_cast<const float *>(smem + P.bias) + stage * 4 * kMaxDim;
 #pragma unroll 1
@@ -219,7 +270,10 @@ rev_fwd_tc_kernel(const RevShape s, const RevParams p, const T *__restrict__ x, 
                 const bool last = k == s.blocks - 1;
                 stream_epilogue<T, BIAS>(taddr + out_col, seat, s.half, bias + (2 * branch + 1) * kMaxDim, u_tile,
                                          last ? y_row + branch * s.half : nullptr, live);
-                if (branch == 1) async_tile_wait();  // next block's weights have landed
+                if (branch == 1) {  // next block's weights have landed
+                    if (!use_tma) async_tile_wait();
+                    else if (more) ring_wait(ring_bars, step + 1, &abort_flag);
+                }
                 publish_tiles();
             }
         }
@@ -231,6 +285,11 @@ rev_fwd_tc_kernel(const RevShape s, const RevParams p, const T *__restrict__ x, 
 // ---- backward ----------------------------------------------------------------------------------
 
 // One weight-gradient accumulator (M = 64 layout) out of TMEM, added into this CTA's private copy.
+// The copy of a matrix is stored [column / 4][row][column % 4]: the 16 lanes of a warp that hold rows
+// m .. m + 15 of one column quad then add to 256 contiguous bytes (8 full sectors per instruction
+// instead of 16 half-used ones), which is what the L2's reduction rate is counted in.
+__host__ __device__ inline int dw_private_index(int row, int col) { return ((col >> 2) * 64 + row) * 4 + (col & 3); }
+
 __device__ __forceinline__ void flush_dw_private(uint32_t taddr, const Seat &seat, int out_dim, int in_dim, float *dst) {
     const int n = in_dim / kGroups, first = seat.group * (n / 8);  // this thread's columns / first 8-column piece
     const int lane = threadIdx.x & 31;
@@ -239,10 +298,9 @@ __device__ __forceinline__ void flush_dw_private(uint32_t taddr, const Seat &sea
     // fire-and-forget vector reductions: no round trip to wait for, and nobody else touches this copy
     for_each_piece(taddr + seat.group * n, n, [&](int u, const uint32_t(&piece)[8]) {
         if (owner) {
-            float *q = dst + m * 64 + 8 * (first + u);
 #pragma unroll
             for (int h = 0; h < 2; ++h)
-                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(q + 4 * h),
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + dw_private_index(m, 8 * (first + u) + 4 * h)),
                              "f"(__uint_as_float(piece[4 * h])), "f"(__uint_as_float(piece[4 * h + 1])),
                              "f"(__uint_as_float(piece[4 * h + 2])), "f"(__uint_as_float(piece[4 * h + 3]))
                              : "memory");
@@ -252,7 +310,8 @@ __device__ __forceinline__ void flush_dw_private(uint32_t taddr, const Seat &sea
 
 template <typename T, int ACT>
 __global__ void __launch_bounds__(kTcThreads, 1)
-rev_bwd_tc_kernel(const RevShape s, const RevParams p, const T *__restrict__ y, long long y_stride,
+rev_bwd_tc_kernel(const RevShape s, const RevParams p, const __grid_constant__ RevWeightMaps maps, const int use_tma,
+                  const T *__restrict__ y, long long y_stride,
                   const T *__restrict__ go, long long go_stride, T *__restrict__ gx, long long gx_stride,
                   T *__restrict__ x_rec, long long xr_stride, float *__restrict__ workspace, long long n_rows) {
     extern __shared__ unsigned char smem_raw[];
@@ -264,16 +323,36 @@ rev_bwd_tc_kernel(const RevShape s, const RevParams p, const T *__restrict__ y, 
     constexpr int bf16 = std::is_same<T, __half>::value ? 0 : 1;
     unsigned char *u_tile = smem, *h_tile = smem + kTileBytes, *dy_tile = smem + 2 * kTileBytes, *dz_tile = smem + 3 * kTileBytes;
 
-    if (threadIdx.x == 0) abort_flag = 0;
+    __shared__ __align__(8) unsigned long long ring_bars[2];
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&ring_bars[0])), "r"(1u) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&ring_bars[1])), "r"(1u) : "memory");
+    }
     for (int e = threadIdx.x; e < 4 * kTileBytes / 16; e += kTcThreads) reinterpret_cast<uint4 *>(smem)[e] = make_uint4(0, 0, 0, 0);
     const long long n_tiles = (n_rows + kTileRows - 1) / kTileRows;
-    if (static_cast<long long>(blockIdx.x) < n_tiles) prefetch_weights<T>(smem, P, s, p, s.blocks - 1, 0);
-    const uint32_t tmem = cta_setup(&tmem_holder, &mbar, P.tmem_cols);
+    if (!use_tma && static_cast<long long>(blockIdx.x) < n_tiles) prefetch_weights<T>(smem, P, s, p, s.blocks - 1, 0);
+    const uint32_t tmem = cta_setup(&tmem_holder, &mbar, P.tmem_cols);  // publishes the barrier inits
+    if (use_tma && static_cast<long long>(blockIdx.x) < n_tiles) {
+        prefetch_weights_tma<T>(smem, P, s, p, maps, ring_bars, s.blocks - 1, 0);
+        ring_wait(ring_bars, 0, &abort_flag);
+    }
     const uint32_t bar = smem_addr(&mbar);
     const Seat seat;
     const uint32_t taddr = tmem + seat.lane_base;
     uint32_t phase = 0;
     int step = 0;
+    // Weight gradients of a pass stay in TMEM until the NEXT pass has issued its first GEMMs: the flush
+    // (tcgen05.ld + vector reductions, ~1 200 cycles) then runs under those GEMMs instead of before them.
+    float *pending_dw1 = nullptr, *pending_dw2 = nullptr;
+    auto flush_pending = [&]() {
+        if (pending_dw1) {
+            flush_dw_private(taddr + kDW1, seat, s.hid, s.half, pending_dw1);
+            flush_dw_private(taddr + kDW2, seat, s.half, s.hid, pending_dw2);
+            pending_dw1 = pending_dw2 = nullptr;
+        }
+    };
+    TH_TRACE_BEGIN
     float *cta_acc = workspace + static_cast<size_t>(blockIdx.x) * rev_cta_floats(s);
     // instruction descriptors: forward-type, dgrad (B MN-major), reconstruction (A negated), wgrad (both MN-major, M = 64)
     const uint32_t id_z = instr_desc(128, s.hid, bf16, 0, 0);
@@ -301,8 +380,11 @@ rev_bwd_tc_kernel(const RevShape s, const RevParams p, const T *__restrict__ y, 
 
         for (int k = s.blocks - 1; k >= 0 && !abort_flag; --k, ++step) {
             const int stage = step & 1;
-            if (k > 0 || tile + gridDim.x < n_tiles)
-                prefetch_weights<T>(smem, P, s, p, k > 0 ? k - 1 : s.blocks - 1, stage ^ 1);
+            const bool more = k > 0 || tile + gridDim.x < n_tiles;
+            if (more) {
+                if (use_tma) prefetch_weights_tma<T>(smem, P, s, p, maps, ring_bars, k > 0 ? k - 1 : s.blocks - 1, stage ^ 1);
+                else prefetch_weights<T>(smem, P, s, p, k > 0 ? k - 1 : s.blocks - 1, stage ^ 1);
+            }
             const unsigned char *w = smem + P.ring + stage * kStageBytes;
             float *block_acc = cta_acc + static_cast<size_t>(k) * 4 * kMatFloats;
 #pragma unroll 1
@@ -313,14 +395,20 @@ rev_bwd_tc_kernel(const RevShape s, const RevParams p, const T *__restrict__ y, 
                 const uint32_t w1 = smem_addr(w + m1 * kWTileBytes), w2 = smem_addr(w + m2 * kWTileBytes);
                 const uint32_t out_col = pass == 0 ? kS2 : kS1, in_d_col = pass == 0 ? kD1 : kD2;
                 bool leader = false;
+                TH_STAMP(90);
                 // step A: z = U . W1^T and dh = DY . W2 together
                 if (threadIdx.x < 32) {
                     leader = elect_one();
                     tc_fence_after();
                     issue_gemm(leader, tmem + kZ, smem_addr(u_tile), 32, w1, 32, s.half / 16, id_z, false);
                     issue_gemm(leader, tmem + kDH, smem_addr(dy_tile), 32, w2, 2048, s.half / 16, id_dh, false);
+                    if (leader) mma_commit(bar);
+                    __syncwarp();
                 }
-                commit_and_wait(leader, bar, phase, &abort_flag);
+                TH_STAMP(91);
+                flush_pending();  // the previous pass's weight gradients, while the GEMMs above run
+                cta_wait_mma(bar, phase, &abort_flag);
+                TH_STAMP(92);
                 {
                     // h = act(z) first (also the ReLU mask), then dz = dh where h > 0
                     const int n = s.hid / kGroups, first = seat.group * (n / 8);
@@ -342,7 +430,9 @@ rev_bwd_tc_kernel(const RevShape s, const RevParams p, const T *__restrict__ y, 
                         st_shared_16(dz_row + off, g);
                     });
                 }
+                TH_STAMP(93);
                 publish_tiles();
+                TH_STAMP(94);
                 // step B: undo the branch, push the gradient through, form both weight gradients
                 if (threadIdx.x < 32) {
                     leader = elect_one();
@@ -352,14 +442,22 @@ rev_bwd_tc_kernel(const RevShape s, const RevParams p, const T *__restrict__ y, 
                     issue_gemm(leader, tmem + kDW2, smem_addr(dy_tile), 2048, smem_addr(h_tile), 2048, kTileRows / 16, id_dw2, false);
                     issue_gemm(leader, tmem + kDW1, smem_addr(dz_tile), 2048, smem_addr(u_tile), 2048, kTileRows / 16, id_dw1, false);
                 }
+                TH_STAMP(95);
                 commit_and_wait(leader, bar, phase, &abort_flag);
+                TH_STAMP(96);
                 // next pass: its input is the stream just reconstructed, its output gradient the one just updated
                 stream_epilogue<T, false>(taddr + out_col, seat, s.half, nullptr, u_tile, nullptr, false);
                 stream_epilogue<T, false>(taddr + in_d_col, seat, s.half, nullptr, dy_tile, nullptr, false);
-                flush_dw_private(taddr + kDW1, seat, s.hid, s.half, block_acc + m1 * kMatFloats);
-                flush_dw_private(taddr + kDW2, seat, s.half, s.hid, block_acc + m2 * kMatFloats);
-                if (pass == 1) async_tile_wait();
+                TH_STAMP(97);
+                pending_dw1 = block_acc + m1 * kMatFloats;
+                pending_dw2 = block_acc + m2 * kMatFloats;
+                TH_STAMP(98);
+                if (pass == 1) {  // next block's weights have landed
+                    if (!use_tma) async_tile_wait();
+                    else if (more) ring_wait(ring_bars, step + 1, &abort_flag);
+                }
                 publish_tiles();
+                TH_STAMP(99);
             }
         }
         // the stream is now the reconstructed input, the gradient stream the input gradient
@@ -377,6 +475,11 @@ rev_bwd_tc_kernel(const RevShape s, const RevParams p, const T *__restrict__ y, 
             tc_fence_before();
             __syncthreads();
         }
+    }
+    TH_TRACE_END;
+    if (!abort_flag) {
+        tc_fence_after();
+        flush_pending();
     }
     if (abort_flag) g_tc_status = 1;
     cta_teardown(tmem, P.tmem_cols);
@@ -396,8 +499,9 @@ __global__ void rev_grad_reduce_tc_kernel(const RevShape s, const float *__restr
         const int row = static_cast<int>((e % kMatFloats) / 64), col = static_cast<int>(e % 64);
         const int out_dim = (m & 1) ? s.half : s.hid, in_dim = (m & 1) ? s.hid : s.half;
         if (row >= out_dim || col >= in_dim || !dw[m]) continue;
+        const size_t at = (e / kMatFloats) * kMatFloats + dw_private_index(row, col);
         float sum = 0.f;
-        for (int c = 0; c < n_ctas; ++c) sum += workspace[c * per_cta + e];
+        for (int c = 0; c < n_ctas; ++c) sum += workspace[c * per_cta + at];
         dw[m][(static_cast<size_t>(k) * out_dim + row) * in_dim + col] = from_float<T>(sum);
     }
 }
@@ -421,6 +525,23 @@ int smem_request(const RevTcPlan &P, int ctas) {
     return need > floor_bytes ? need : floor_bytes;
 }
 
+// Tensor maps of the four stacked weight arrays (box = 64 columns x one block's rows); 0 when one of
+// them cannot be described (then the kernels stage the weights with cp.async) or TH_MLP_NO_TMA=1.
+int make_rev_maps(RevWeightMaps &maps, const RevShape &s, const RevParams &p) {
+    memset(&maps, 0, sizeof(maps));
+    static const bool off = [] {
+        const char *v = getenv("TH_MLP_NO_TMA");
+        return v && v[0] == '1';
+    }();
+    if (off) return 0;
+    const void *w[4] = {p.w_f1, p.w_f2, p.w_g1, p.w_g2};
+    for (int m = 0; m < 4; ++m) {
+        const int rows = (m & 1) ? s.half : s.hid, cols = (m & 1) ? s.hid : s.half;
+        if (!make_map(&maps.m[m], w[m], static_cast<long long>(s.blocks) * rows, cols, rows)) return 0;
+    }
+    return 1;
+}
+
 template <typename T, int ACT, bool BIAS>
 int launch_rev_fwd_t(const RevShape &s, const RevParams &p, const void *x, int64_t x_stride, void *y, int64_t y_stride,
                      int64_t rows, cudaStream_t stream) {
@@ -432,8 +553,10 @@ int launch_rev_fwd_t(const RevShape &s, const RevParams &p, const void *x, int64
                              "cudaFuncSetAttribute(rev_fwd_tc_kernel)")) return rc;
     const long long tiles = (rows + kTileRows - 1) / kTileRows;
     const long long cap = static_cast<long long>(sm_count()) * ctas;
+    RevWeightMaps maps;
+    const int use_tma = make_rev_maps(maps, s, p);
     kernel<<<static_cast<unsigned>(tiles < cap ? tiles : cap), kTcThreads, smem, stream>>>(
-        s, p, static_cast<const T *>(x), x_stride, static_cast<T *>(y), y_stride, rows);
+        s, p, maps, use_tma, static_cast<const T *>(x), x_stride, static_cast<T *>(y), y_stride, rows);
     return launch_status("rev_fwd_tc_kernel launch");
 }
 
@@ -464,9 +587,11 @@ int launch_rev_bwd_t(const RevShape &s, const RevParams &p, const void *y, int64
     auto kernel = rev_bwd_tc_kernel<T, ACT>;
     if (int rc = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
                              "cudaFuncSetAttribute(rev_bwd_tc_kernel)")) return rc;
-    kernel<<<n_ctas, kTcThreads, smem, stream>>>(s, p, static_cast<const T *>(y), y_stride, static_cast<const T *>(go),
-                                                go_stride, static_cast<T *>(gx), gx_stride, static_cast<T *>(x_rec),
-                                                xr_stride, workspace, rows);
+    RevWeightMaps maps;
+    const int use_tma = make_rev_maps(maps, s, p);
+    kernel<<<n_ctas, kTcThreads, smem, stream>>>(s, p, maps, use_tma, static_cast<const T *>(y), y_stride,
+                                                static_cast<const T *>(go), go_stride, static_cast<T *>(gx), gx_stride,
+                                                static_cast<T *>(x_rec), xr_stride, workspace, rows);
     if (int rc = launch_status("rev_bwd_tc_kernel launch")) return rc;
     const size_t mat_total = static_cast<size_t>(s.blocks) * 4 * kMatFloats;
     rev_grad_reduce_tc_kernel<T><<<static_cast<unsigned>((mat_total + 255) / 256), 256, 0, stream>>>(
@@ -517,3 +642,15 @@ extern "C" int th_rev_tc_status(void) {
     if (cudaMemcpyFromSymbol(&status, th::g_tc_status, sizeof(int)) != cudaSuccess) return -1;
     return status;
 }
+
+#ifdef TH_TC_TRACE
+extern "C" int th_rev_trace_read(long long *out_host, int max_pairs) {
+    int n = 0;
+    cudaMemcpyFromSymbol(&n, th::g_trace_n, sizeof(int));
+    if (n > max_pairs) n = max_pairs;
+    cudaMemcpyFromSymbol(out_host, th::g_trace, sizeof(long long) * 2 * n);
+    int zero = 0;
+    cudaMemcpyToSymbol(th::g_trace_n, &zero, sizeof(int));
+    return n;
+}
+#endif
