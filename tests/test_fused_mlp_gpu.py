@@ -171,6 +171,21 @@ def test_many_row_tiles_per_cta(dtype, depth, d_hid):
             assert nerr(gg, w) <= (tight if name == "y" else 10 * tight), f"{name}: {nerr(gg, w)}"
 
 
+@pytest.mark.parametrize("rows", [1, 127, 128, 129, 4 * 128 + 1])
+def test_row_count_edges_on_the_tensor_core_path(rows):
+    # aligned 32 -> 64 -> 64 -> 16 without biases: the TMA-fed kernels, whose last tile is partly
+    # (or almost wholly) past the end of the batch
+    dtype = torch.float16
+    p = make_params(32, 64, 16, 2, dtype, bias=False, seed=rows)
+    g = torch.Generator().manual_seed(rows)
+    x = torch.randn(1, rows, 32, generator=g).to(dtype)
+    go = torch.randn(1, rows, 16, generator=g).mul(1e-1).to(dtype).float()
+    want, got = run_both(x, p, go, "relu", rounded=True)
+    for name, w, gg in zip(NAMES, want, got):
+        if w is not None:
+            assert gg.shape == w.shape and nerr(gg, w) <= (0.5 if name == "dx" else 1e-2), f"{name}: {nerr(gg, w)}"
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_baseline_configuration_full_size(dtype):
     # 2^20 rows, 32 -> 4 hidden layers of 64 (ReLU) -> 16, no bias, grad_out ~ 1e-2 N(0, 1)
