@@ -2,7 +2,7 @@ r"""Benchmark of the fused neural-field operators on B200.
 
     python bench.py --gpus N --steps K --warmup W [--workload NAME] [--impl reference]
 
-Default workload ``train_step`` is BASELINE configuration 3: per GPU 2^21 uniform 3-D points ->
+Default workload ``train_step`` is benchmark configuration 3: per GPU 2^21 uniform 3-D points ->
 hash encoding (16 levels x 2 features, T = 2^19, 16..2048, float16 table) -> fused MLP
 32 -> 64 -> 64 -> 16 (ReLU, float16) -> MSE -> backward -> gradient all-reduce (NCCL) -> Adam.
 A "step" is one such pass over one batch; ``value`` is points per second over all ranks with the
@@ -136,7 +136,7 @@ def clustered_points(n, gen, device):
 
 
 class TrainStep:
-    r"""BASELINE configuration 3."""
+    r"""benchmark configuration 3."""
 
     name = "cfg3: 2^21 pts/GPU, hash L16 F2 T2^19 16..2048 fp16 -> MLP 32-64-64-16 fp16 -> MSE -> allreduce -> Adam"
     dtype = "f16"

@@ -11,7 +11,7 @@ layer is never activated (kernel.py:250).
 
 Activations follow ``triton_helpers/ops.py:38-66``: ``relu``, ``silu``, ``relu2(z) = max(z, 0) * z``
 and ``none``.  Everything is evaluated in float32 from the (possibly fp16/bf16-valued)
-inputs, which is the comparison BASELINE configuration 1 asks for.
+inputs, which is the comparison benchmark configuration 1 asks for.
 """
 from typing import Optional, Tuple
 

@@ -1,6 +1,6 @@
 r"""CPU port of the neural-field training step.  TEST INFRASTRUCTURE / CPU BASELINE ONLY.
 
-Composes the oracles of the two layers the way BASELINE configuration 3 describes: hash
+Composes the oracles of the two layers the way benchmark configuration 3 describes: hash
 encoding (``oracle.hash_encoding.encode``, the restatement of the reference's
 ``_cpu_hash_encoding``, ``triton_helpers/layers/hash_encoding/kernel.py:482-502``) -> float32 MLP
 (``oracle.fused_mlp.forward``, the reference's test MLP,

@@ -2,9 +2,9 @@ r"""Parity of the CUDA fused MLP with a float32 torch computation (the oracle).
 
 Shapes, seeds and tolerances follow the reference's tests
 (tests/test_layers/test_fully_fused_mlp.py:38-107 forward, :231-369 backward, :372-415 module):
-``assert_close(rtol=1e-2, atol=1e-2)`` against a float32 ``nn.Linear`` chain.  The BASELINE
+``assert_close(rtol=1e-2, atol=1e-2)`` against a float32 ``nn.Linear`` chain.  The benchmark
 configuration (2^20 rows, 32 -> 4 x 64 -> 16, no bias) is checked with the normalised error
-``max|a-b| / max|b| <= 1e-2`` the north star states.
+``max|a-b| / max|b| <= 1e-2`` that its specification states.
 """
 import pytest
 import torch

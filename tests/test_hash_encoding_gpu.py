@@ -2,7 +2,7 @@ r"""Parity of the CUDA hash encoding with the CPU oracle and the reference's gol
 
 Every test goes through the Python layer, which calls the C ABI (``th_hash_fwd`` /
 ``th_hash_bwd`` / ``th_hash_debug_indices``) with no other compute path available.
-Tolerances (BASELINE north star): indices bit-exact; float32 forward ``max|a-b| / max|b|
+Tolerances (the benchmark specification): indices bit-exact; float32 forward ``max|a-b| / max|b|
 <= 1e-6``; float32 table gradient ``<= 1e-5`` (atomics reorder the sums); float16 tables
 use the reference's own test tolerances (``atol=1e-2`` forward,
 ``atol=1e-3*N, rtol=1e-2`` backward; tests/test_layers/test_hash_encoding.py:432,489).
@@ -129,7 +129,7 @@ def test_forward_matches_reference_fixtures(golden):
 @pytest.mark.parametrize(
     "N,D,F,T,L,lo,hi",
     [
-        (65536, 3, 2, 2**19, 16, 16, 2048),  # BASELINE configuration 0
+        (65536, 3, 2, 2**19, 16, 16, 2048),  # benchmark configuration 0
         (10001, 3, 4, 2**16, 16, 16, 4096),
         (4099, 2, 2, 2**12, 8, 4, 512),
         (1000, 1, 1, 2**10, 4, 8, 256),

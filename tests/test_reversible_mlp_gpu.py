@@ -4,7 +4,7 @@ The reference has no reversible operator, so parity is defined by ``oracle/rever
 alone (unpinned by the reference).  Tolerances: outputs and parameter gradients within 1e-2
 (float16) / 3e-2 (bfloat16: 8-bit mantissa) normalised error of the float32 computation; the
 tight comparison is against the oracle that rounds where the kernels round.  The
-size-independent property at the full BASELINE size is reconstruction: the backward pass must
+size-independent property at the full benchmark size is reconstruction: the backward pass must
 recover the stack's input from its output.
 """
 import pytest
@@ -54,7 +54,7 @@ def to_cuda(ts):
 @pytest.mark.parametrize(
     "rows,d_model,hidden,blocks,bias,activation",
     [
-        (1000, 128, 64, 8, False, "relu"),  # BASELINE configuration 2 at a size the oracle finishes quickly
+        (1000, 128, 64, 8, False, "relu"),  # benchmark configuration 2 at a size the oracle finishes quickly
         (300, 128, 64, 2, True, "relu"),
         (257, 64, 32, 3, True, "silu"),
         (129, 32, 16, 1, False, "none"),

@@ -1,6 +1,6 @@
 r"""Neural-field training step: hash encoding -> fused MLP -> MSE -> backward -> gradient sum -> Adam.
 
-The step BASELINE configuration 3 describes, built only from this package's operators.  It
+The step benchmark configuration 3 describes, built only from this package's operators.  It
 has no counterpart in triton_helpers (which stops at the two layers); the layers it drives are
 the drop-in ``HashEncoding`` and ``FullyFusedMLP`` modules, so everything between the coordinates
 and the parameter update runs in the hand-written kernels: ``th_hash_fwd``, ``th_mlp_fwd``,
@@ -49,7 +49,7 @@ class NeuralFieldTrainer(nn.Module):
 
     Args:
         encoding, mlp: the two layers (moved to the device and dtype the caller wants; float16
-            tables and weights for BASELINE configuration 3).
+            tables and weights for benchmark configuration 3).
         lr, betas, eps: Adam hyper-parameters.
         grad_out_scale: the MLP receives ``(pred - target) * grad_out_scale`` as its output
             gradient, i.e. the loss is scaled so 16-bit gradients neither underflow nor overflow;
