@@ -310,6 +310,9 @@ def test_backward_all_points_identical():
         (3, 1, 2**14, 4, 4, 64, torch.float32),
         (3, 2, 2**19, 16, 16, 2048, torch.float16),
         (3, 8, 2**14, 4, 16, 128, torch.bfloat16),
+        (3, 8, 2**14, 4, 16, 128, torch.float32),  # 32-byte rows: two 16-byte compare-and-swaps
+        (3, 4, 2**14, 4, 16, 128, torch.float16),  # 8-byte rows
+        (3, 1, 2**14, 4, 16, 64, torch.float16),  # 2-byte rows: native half add
         (3, 4, 2**21, 8, 16, 1024, torch.float32),  # 144 MB of levels: cut into cache-sized passes
     ],
 )
