@@ -167,13 +167,25 @@ class TrainStep:
 
     # end to end: batch arrives from pinned host memory, loss goes back
     def prepare_e2e(self):
-        self.host = [(self.coords.cpu().pin_memory(), self.targets.cpu().pin_memory()) for _ in range(2)]
-        self.dev = [(torch.empty_like(self.coords), torch.empty_like(self.targets)) for _ in range(2)]
+        # One pinned host buffer and one device buffer per slot hold [coordinates | targets], so a batch
+        # crosses the host link as a single copy (two slots: the next batch copies in while this one computes).
+        n_coord = self.coords.numel() * 4
+        n_target = self.targets.numel() * 2
+        self.h2d_bytes = n_coord + n_target
+        self.host, self.dev_raw, self.dev = [], [], []
+        for _ in range(2):
+            host = torch.empty(self.h2d_bytes, dtype=torch.uint8).pin_memory()
+            host[:n_coord].view(torch.float32).copy_(self.coords.cpu().reshape(-1))
+            host[n_coord:].view(torch.float16).copy_(self.targets.cpu().reshape(-1))
+            raw = torch.empty(self.h2d_bytes, dtype=torch.uint8, device=self.device)
+            self.host.append(host)
+            self.dev_raw.append(raw)
+            self.dev.append((raw[:n_coord].view(torch.float32).view_as(self.coords),
+                             raw[n_coord:].view(torch.float16).view_as(self.targets)))
         self.copy_stream = torch.cuda.Stream(device=self.device)
         self.ready = [torch.cuda.Event() for _ in range(2)]
         self.consumed = [torch.cuda.Event() for _ in range(2)]
         self.loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
-        self.h2d_bytes = self.coords.numel() * 4 + self.targets.numel() * 2
         self.d2h_bytes = 4
         self.slot = 0
         self._prefetch(0)
@@ -181,8 +193,7 @@ class TrainStep:
     def _prefetch(self, slot):
         with torch.cuda.stream(self.copy_stream):
             self.copy_stream.wait_event(self.consumed[slot])
-            self.dev[slot][0].copy_(self.host[slot][0], non_blocking=True)
-            self.dev[slot][1].copy_(self.host[slot][1], non_blocking=True)
+            self.dev_raw[slot].copy_(self.host[slot], non_blocking=True)
             self.ready[slot].record(self.copy_stream)
 
     def step_e2e(self):
