@@ -16,11 +16,18 @@ launches): their device work is shorter than the Python around it.  The per-kern
 the roofline always come from an eager pass with CUDA events around every C-ABI call.
 
 One JSON line is printed by rank 0.  ``--impl reference`` times the CPU port of the same step
-(``oracle/``: the restatement of the reference's torch CPU path) on the host cores instead.
+(``oracle/``: the restatement of the reference's torch CPU path) on the host cores instead, on the
+same 2^21-point batch.
+
+The run fails (non-zero exit, no JSON line) when any rank's loss is not finite after a timed leg,
+when the optimiser skipped non-finite gradients, or when a tensor-core kernel gave up on a wait.
 """
 import argparse
+import glob
 import json
+import math
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -35,15 +42,33 @@ import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
 METRIC = "fwd+bwd points/sec (hash-enc + fused MLP)"
+TRAIN_POINTS = 2**21  # per GPU per step (benchmark configuration 3)
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu captures summarised under
-# profiles/ (hash_bwd_kernel_cfg3.md, hash_fwd_kernel_cfg3.md, mlp_bwd_pipe_kernel_cfg3.md,
-# mlp_fwd_pipe_kernel_cfg3.md), all taken on the full cfg 3 workload; th_hash_bwd is the sum of its two
-# kernels.  Other workloads have no capture yet: traffic is reported as null there.
-NCU_TRAFFIC_BYTES = {
-    "train_step": {"th_hash_bwd": 355.9e6, "th_hash_fwd": 131.4e6, "th_mlp_bwd": 298.8e6, "th_mlp_fwd": 174.6e6, "th_mlp_fwd_mse": 239.9e6},
-}
 L2_BYTES = 126 * 1024 * 1024
+
+# ncu figures are not typed in here: a summary under profiles/ that wants one of its captured figures
+# quoted beside the timed number carries a line
+#   bench-record: workload=<name> entry=<C-ABI entry> dram_bytes_per_launch=<int> l2_requests_per_launch=<int>
+# and the JSON line names the file it took them from.  No such line -> null.
+RECORD = re.compile(r"bench-record:\s*(.*)")
+
+
+def ncu_records(workload):
+    found = {}
+    for path in sorted(glob.glob(os.path.join(ROOT, "profiles", "*.md"))):
+        try:
+            text = open(path).read()
+        except OSError:
+            continue
+        for m in RECORD.finditer(text):
+            fields = dict(kv.split("=", 1) for kv in m.group(1).split() if "=" in kv)
+            if fields.get("workload") == workload and "entry" in fields:
+                rec = {"source": os.path.relpath(path, ROOT)}
+                for key in ("dram_bytes_per_launch", "l2_requests_per_launch"):
+                    if key in fields:
+                        rec[key] = float(fields[key])
+                found[fields["entry"]] = rec
+    return found
 
 
 def measured_peaks():
@@ -141,7 +166,7 @@ class TrainStep:
     name = "cfg3: 2^21 pts/GPU, hash L16 F2 T2^19 16..2048 fp16 -> MLP 32-64-64-16 fp16 -> MSE -> allreduce -> Adam"
     dtype = "f16"
 
-    def __init__(self, device, rank, points, backward_passes=None):
+    def __init__(self, device, rank, points, args):
         from triton_helpers_b200.layers.fully_fused_mlp import FullyFusedMLP
         from triton_helpers_b200.layers.hash_encoding import HashEncoding
         from triton_helpers_b200.training import NeuralFieldTrainer
@@ -153,17 +178,24 @@ class TrainStep:
             enc.embeddings.uniform_(-1e-4, 1e-4)
         mlp = FullyFusedMLP(32, 64, 16, depth=2, bias=False)
         self.trainer = NeuralFieldTrainer(enc.to(device).half(), mlp.to(device).half(), lr=1e-2, betas=(0.9, 0.99), eps=1e-15,
-                                          backward_passes=backward_passes)
+                                          backward_passes=args.backward_passes)
         gen = torch.Generator(device=device).manual_seed(1234 + rank)  # a different batch per rank
         self.coords = torch.rand(points, 3, device=device, generator=gen)
         self.targets = torch.rand(points, 16, device=device, generator=gen).half()
         self.table_elems = enc.embeddings.numel()
         self.units = points
-        self.gathers_per_step = points * 16 * 8  # one table row per corner per level
         self.host = None
+        self.last_loss = None
 
     def step(self):
-        return self.trainer.step(self.coords, self.targets)
+        self.last_loss = self.trainer.step(self.coords, self.targets)
+        return self.last_loss
+
+    def skipped(self):
+        return self.trainer.skipped_elements()
+
+    def collective_buffer(self):
+        return self.trainer._state.flat_grad
 
     # end to end: batch arrives from pinned host memory, loss goes back
     def prepare_e2e(self):
@@ -205,19 +237,33 @@ class TrainStep:
         self.loss_host.copy_(loss, non_blocking=True)
         self.slot ^= 1
 
+    def h2d_alone(self, world):
+        r"""The batch's host-to-device copy by itself, every rank at once (what the host link gives N ranks):
+        GB/s per rank (the slowest rank's) and summed over ranks."""
+        copy = lambda: self.dev_raw[0].copy_(self.host[0], non_blocking=True)  # noqa: E731
+        for _ in range(3):
+            copy()
+        reps = 20
+        ms = timed_region(copy, reps, world) / reps
+        per_rank = self.h2d_bytes / (ms * 1e-3) / 1e9
+        return {"ms": ms, "gbs_per_rank": per_rank, "gbs_all_ranks": per_rank * world, "reps": reps}
+
     def work(self):
         S, n = 2, self.points
         mlp_flops = 2 * (32 * 64 + 64 * 64 + 64 * 16)
+        enc = hash_bytes_per_point(16, 2, S) * n
         return {
-            "th_hash_fwd": ("hbm", hash_bytes_per_point(16, 2, S) * n),
-            "th_hash_bwd": ("hbm", hash_bytes_per_point(16, 2, S) * n),
+            "th_hash_fwd": ("hbm", enc),
+            "th_hash_bwd": ("hbm", enc),
+            "th_field_fwd": ("hbm", enc),   # encoding + MLP forward + loss in one kernel: the encoding's bytes bound it
+            "th_field_bwd": ("hbm", enc),   # MLP backward + encoding backward in one kernel
             "th_mlp_fwd": ("tensor", mlp_flops * n),
             "th_mlp_fwd_mse": ("tensor", mlp_flops * n),  # forward with the loss fused into its last layer
             "th_mlp_bwd": ("tensor", 2 * mlp_flops * n),
             "th_mse_grad": ("hbm", 3 * S * 16 * n),
+            "th_scale_cast": ("hbm", 6 * 7168),
             "th_adam_step": ("hbm", (3 * S + 16) * self.table_elems),
         }
-
 
 
 class HashOnly:
@@ -225,6 +271,9 @@ class HashOnly:
 
     def __init__(self, device, rank, key):
         from triton_helpers_b200.layers.hash_encoding import hash_encoding
+        self.key = key
+        self.allreduce = dist.is_initialized() and dist.get_world_size() > 1 and key == "contention"
+        self.kernel_only_ms = None
         from triton_helpers_b200.layers.hash_encoding.helpers import level_geometry
 
         c = HASH_CFG[key]
@@ -237,13 +286,28 @@ class HashOnly:
         self.table = ((torch.rand(geo.total_rows, c["feats"], device=device, generator=gen) * 2 - 1) * 1e-4).requires_grad_(True)
         self.go = torch.randn(c["points"], 16 * c["feats"], device=device, generator=gen)
         self.units = c["points"]
-        self.gathers_per_step = c["points"] * 16 * 8
 
     def step(self):
         c = self.c
         out = self.fn(self.x, self.table, None, None, c["cap"], 16, c["n_max"], 16)
         (g,) = torch.autograd.grad(out, self.table, self.go)
+        if self.allreduce:
+            dist.all_reduce(g)  # cfg 4 data parallel: the 681 MB float32 table gradient, summed over ranks every step
         return g
+
+    def collective_buffer(self):
+        return torch.empty_like(self.table) if self.allreduce else torch.empty(0, device=self.device)
+
+    def extra(self):
+        # kernel-only number next to the one with the all-reduce
+        if not self.allreduce:
+            return {}
+        self.allreduce = False
+        for _ in range(3):
+            self.step()
+        ms = timed_region(self.step, 10, dist.get_world_size()) / 10
+        self.allreduce = True
+        return {"kernel_only": {"ms_per_step": ms, "value": self.units * dist.get_world_size() / (ms * 1e-3), "unit": "points/s"}}
 
     def work(self):
         b = hash_bytes_per_point(16, self.c["feats"], 4) * self.units
@@ -303,9 +367,9 @@ class ReversibleOnly:
 
 
 
-def build_workload(name, device, rank, backward_passes=None):
+def build_workload(name, device, rank, args):
     if name == "train_step":
-        return TrainStep(device, rank, 2**21, backward_passes)
+        return TrainStep(device, rank, TRAIN_POINTS, args)
     if name in HASH_CFG:
         return HashOnly(device, rank, name)
     if name == "mlp":
@@ -319,7 +383,7 @@ def build_workload(name, device, rank, backward_passes=None):
 
 
 def cpu_training_step_rate(steps, warmup, points):
-    r"""points/s of the CPU port of the training step on all host threads (bounded sample)."""
+    r"""points/s of the CPU port of the training step on all host threads."""
     from oracle.training_step import CpuNeuralField, make_batch
 
     threads = os.cpu_count() or 1
@@ -376,18 +440,31 @@ def cpu_operator_rate(workload):
     return n * reps / (time.perf_counter() - t0), threads, sample
 
 
+def workload_config(name):
+    r"""The `config` object of the JSON line: identical for the GPU arm and the CPU arm of a workload."""
+    return {
+        "workload": name,
+        "units_per_gpu_per_step": TRAIN_POINTS,
+        "l2": "per-step inputs and intermediates (25 MB coordinates, 67 MB targets, 134 MB features per step) exceed "
+              "the 126 MB L2; no explicit flush",
+    }  # fmt: skip
+
+
 def run_reference(args, rank):
+    r"""The CPU arm: the float32 port of the same step on the same batch size, all host threads.  One step of
+    2^21 points takes a few seconds, so K + W steps end within a few minutes."""
     if rank != 0:
         return
-    points = 2**16
-    rate, threads, ms = cpu_training_step_rate(args.steps, args.warmup, points)
+    rate, threads, ms = cpu_training_step_rate(args.steps, args.warmup, TRAIN_POINTS)
     line = {
         "impl": "reference", "metric": METRIC, "value": rate, "unit": "points/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": TrainStep.name, "arm": "CPU port of the same step (oracle/), float32, host cores only"},
+        "config": workload_config(TrainStep.name),
+        "arm": "CPU port of the same step (oracle/: the reference's torch CPU path restated), float32, host cores only; "
+               "rank 0 alone runs it",
         "cpu_baseline": {"value": rate, "unit": "points/s", "cores": threads, "kind": "port",
-                         "sample": f"{points} points per step (the GPU arm uses 2^21 per GPU)"},
+                         "sample": f"{args.steps} steps of {TRAIN_POINTS} points (the GPU arm's batch per GPU)"},
         "e2e": {"value": rate, "unit": "points/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }  # fmt: skip
@@ -414,33 +491,56 @@ def timed_region(fn, steps, world):
     return float(ms)
 
 
-def l2_probe(device):
-    r"""What the L2 delivers for the encoding's two access patterns, measured with ``th_probe_l2`` on a
-    24 MB buffer (the size of the cfg 3 float16 table): coalesced streaming reads in GB/s, random
-    32-byte-sector gathers and random float16-pair reductions in 1e9 per second.  CUDA events on the
-    launching stream."""
-    import ctypes
+def step_quantiles(fn, reps, world):
+    r"""Per-step device times of `reps` more steps (CUDA events around each): the reference harness's
+    statistic - median with the 20th and 80th percentile (triton_helpers/benchmark.py:153) - max over ranks
+    per percentile."""
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    events = [torch.cuda.Event(enable_timing=True) for _ in range(reps + 1)]
+    events[0].record()
+    for i in range(reps):
+        fn()
+        events[i + 1].record()
+    torch.cuda.synchronize()
+    times = sorted(events[i].elapsed_time(events[i + 1]) for i in range(reps))
+    pick = lambda q: times[min(reps - 1, int(q * reps))]  # noqa: E731
+    q = torch.tensor([pick(0.2), pick(0.5), pick(0.8)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(q, op=dist.ReduceOp.MAX)
+    return {"reps": reps, "p20_ms": float(q[0]), "median_ms": float(q[1]), "p80_ms": float(q[2])}
 
+
+def collective_alone(buffer, reps, world):
+    r"""The step's one collective by itself: all-reduce of the flat gradient buffer, CUDA events, max over ranks."""
+    scratch = torch.zeros_like(buffer)
+    for _ in range(5):
+        dist.all_reduce(scratch)
+    ms = timed_region(lambda: dist.all_reduce(scratch), reps, world) / reps
+    nbytes = scratch.numel() * scratch.element_size()
+    return {"bytes": nbytes, "ms": ms, "reps": reps, "algbw_gbs": nbytes / (ms * 1e-3) / 1e9,
+            "busbw_gbs": nbytes * 2 * (world - 1) / world / (ms * 1e-3) / 1e9}  # fmt: skip
+
+
+def health(world, device, losses, skipped):
+    r"""Stops the run when a loss is not finite on any rank, Adam skipped elements, or a tensor-core kernel
+    reported a wait that ran out."""
     from triton_helpers_b200 import _lib
 
-    buf = torch.empty(24 * 2**20, dtype=torch.uint8, device=device).random_(0, 255)
-    sink = torch.zeros(1, dtype=torch.int32, device=device)
-    lib, stream = _lib.lib(), _lib.stream_ptr(device)
-    out = {}
-    for mode, iters, key, scale in ((0, 40, "stream_gbs", 1e9), (1, 64, "gather_g_per_s", 1e9), (2, 64, "update_g_per_s", 1e9)):
-        work = ctypes.c_int64(0)
-        call = lambda: _lib.check(lib.th_probe_l2(buf.data_ptr(), buf.numel(), mode, iters, sink.data_ptr(), ctypes.byref(work), stream), "th_probe_l2")  # noqa: E731
-        for _ in range(3):
-            call()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(5):
-            call()
-        stop.record()
-        torch.cuda.synchronize()
-        out[key] = work.value * 5 / (start.elapsed_time(stop) * 1e-3) / scale
-    out["buffer_mb"] = 24
-    return out
+    lib = _lib.lib()
+    bad = 0
+    bad |= 1 if any(not math.isfinite(v) for v in losses) else 0
+    bad |= 2 if skipped else 0
+    bad |= 4 if (lib.th_mlp_tc_status() != 0 or lib.th_rev_tc_status() != 0) else 0
+    flag = torch.tensor([bad], dtype=torch.int32, device=device)
+    if world > 1:
+        dist.all_reduce(flag, op=dist.ReduceOp.BOR)
+    bad = int(flag)
+    if bad:
+        reasons = [text for bit, text in ((1, "a loss is not finite"), (2, "Adam skipped non-finite gradients"),
+                                          (4, "a tensor-core kernel gave up on a wait")) if bad & bit]  # fmt: skip
+        raise SystemExit(f"bench.py: invalid run on at least one rank: {'; '.join(reasons)} (losses here: {losses})")
 
 
 def main():
@@ -451,10 +551,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="train_step", choices=["train_step", "hash", "mlp", "reversible", "contention"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--unfused", action="store_true", help="train_step: separate encoding and MLP kernels instead of the fused pair")
     ap.add_argument("--backward-passes", type=int, default=None,
                     help="train_step: run the encoding backward in this many level ranges with the gradient sums overlapped")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="time CUDA-graph replays of the step (auto: single-operator workloads on one GPU)")
+    ap.add_argument("--quantile-reps", type=int, default=100, help="extra steps timed one by one for median / p20 / p80")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -473,12 +575,14 @@ def main():
     device = torch.device("cuda", local_rank)
     _lib.lib()  # fail loudly here if the extension is missing
 
-    wl = build_workload(args.workload, device, rank, args.backward_passes)
+    wl = build_workload(args.workload, device, rank, args)
+    is_train = args.workload == "train_step"
     # the sampler starts before the warm-up (nvidia-smi takes ~100 ms to deliver its first line);
     # the busier half of its samples is what gets summarised
-    use_graph = args.graph == "on" or (args.graph == "auto" and world == 1 and args.workload != "train_step")
+    use_graph = args.graph == "on" or (args.graph == "auto" and world == 1 and not is_train)
     timing = ("eager launches, CUDA events around the K timed steps; per-kernel times from a second pass of K steps "
               "with CUDA events around every C-ABI call (the extra events cost 2-3 % of the step)")
+    losses = []
     with ClockSampler(local_rank) as clocks:
         for _ in range(args.warmup):
             wl.step()
@@ -486,9 +590,12 @@ def main():
         launches_before = _lib.lib().th_launch_count()
         total_ms = timed_region(wl.step, args.steps, world)
         launches = _lib.lib().th_launch_count() - launches_before
+        if is_train:
+            losses.append(float(wl.last_loss))  # the loss of the last device-timed step
         with _lib.KernelTimer() as timer:
             timed_region(wl.step, args.steps, world)
         kernels = timer.summary()
+        graph = None
         if use_graph:
             # The single-operator steps are tens of microseconds of GPU work behind hundreds of
             # microseconds of Python: replaying a captured step measures the kernels, the eager pass
@@ -507,7 +614,11 @@ def main():
                 total_ms = timed_region(graph.replay, args.steps, world)
                 timing = "CUDA-graph replays of one captured step, CUDA events around the timed replays; per-kernel times from an eager pass"
             except Exception as exc:  # noqa: BLE001  (report and keep the eager number)
+                graph = None
                 timing += f" (graph capture failed: {type(exc).__name__}: {exc})"[:300]
+        quantiles = step_quantiles(graph.replay if graph is not None else wl.step, max(args.quantile_reps, 1), world)
+        if is_train:
+            losses.append(float(wl.last_loss))
     clock_summary = clocks.summary()
     ms_per_step = total_ms / args.steps
     value = wl.units * world / (ms_per_step * 1e-3)
@@ -521,13 +632,27 @@ def main():
     bound, amount = work[top]
     calls, top_ms = kernels[top]
     per_launch_s = top_ms / calls * 1e-3
+    per_launch_amount = amount * (args.steps / calls)
     if bound == "hbm":
-        achieved, peak, unit = amount * (args.steps / calls) / per_launch_s / 1e9, peaks["hbm_gbs"], "GB/s"
+        achieved, peak, unit = per_launch_amount / per_launch_s / 1e9, peaks["hbm_gbs"], "GB/s"
     else:
-        achieved, peak, unit = amount * (args.steps / calls) / per_launch_s / 1e12, peaks["tflops"], "TFLOP/s"
+        achieved, peak, unit = per_launch_amount / per_launch_s / 1e12, peaks["tflops"], "TFLOP/s"
+    record = ncu_records(args.workload).get(top, {})
     roofline = {"kernel": top, "bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
-                "traffic": NCU_TRAFFIC_BYTES.get(args.workload, {}).get(top), "peak_source": peaks["source"], "algorithmic_per_launch": amount * (args.steps / calls),
+                "traffic": record.get("dram_bytes_per_launch"), "traffic_source": record.get("source"),
+                "peak_source": peaks["source"], "algorithmic_per_launch": per_launch_amount,
                 "ms_per_launch": per_launch_s * 1e3}  # fmt: skip
+    # The encoding kernels of cfg 0 / 3 run out of L2 (the table never leaves it): what bounds them is the
+    # SM-to-L2 request path, one request per clock per SM.  Requests per launch come from the ncu summary
+    # the record names; the ceiling uses this run's own SM clock.
+    request_roofline = None
+    if record.get("l2_requests_per_launch") and clock_summary.get("sm_mhz"):
+        ceiling = torch.cuda.get_device_properties(device).multi_processor_count * clock_summary["sm_mhz"] * 1e6
+        rate = record["l2_requests_per_launch"] / per_launch_s
+        request_roofline = {"kernel": top, "bound": "sm_to_l2_requests", "achieved": rate / 1e9, "peak": ceiling / 1e9,
+                            "unit": "G requests/s", "frac": rate / ceiling, "requests_per_launch": record["l2_requests_per_launch"],
+                            "source": record["source"],
+                            "peak_source": "SM count x median SM clock of this run (one L2 request per clock per SM)"}  # fmt: skip
 
     e2e = None
     if hasattr(wl, "prepare_e2e"):
@@ -535,46 +660,43 @@ def main():
         for _ in range(args.warmup):
             wl.step_e2e()
         e2e_ms = timed_region(wl.step_e2e, args.steps, world) / args.steps
+        losses.append(float(wl.loss_host[0]))
         e2e = {"value": wl.units * world / (e2e_ms * 1e-3), "unit": "points/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": wl.h2d_bytes, "d2h_bytes_per_step": wl.d2h_bytes,
-               "last_loss": float(wl.loss_host[0])}  # fmt: skip
+               "last_loss": float(wl.loss_host[0]), "h2d_alone": wl.h2d_alone(world)}  # fmt: skip
 
-    # the encoding kernels run out of L2 (cfg 0 / 3): put the cache's own figures beside the HBM roofline
-    l2 = None
-    if rank == 0 and args.workload in ("train_step", "hash", "contention"):
-        l2 = l2_probe(device)
-        fwd = kernels.get("th_hash_fwd")
-        if fwd and hasattr(wl, "gathers_per_step"):
-            l2["hash_fwd_gather_g_per_s"] = wl.gathers_per_step * args.steps / (fwd[1] * 1e-3) / 1e9
-            l2["hash_fwd_frac_of_gather_probe"] = l2["hash_fwd_gather_g_per_s"] / l2["gather_g_per_s"]
-        bwd = kernels.get("th_hash_bwd")
-        if bwd and hasattr(wl, "gathers_per_step"):
-            l2["hash_bwd_update_g_per_s"] = wl.gathers_per_step * args.steps / (bwd[1] * 1e-3) / 1e9
-            l2["hash_bwd_frac_of_update_probe"] = l2["hash_bwd_update_g_per_s"] / l2["update_g_per_s"]
+    health(world, device, losses, wl.skipped() if is_train else 0)
+
+    collective = None
+    if world > 1 and hasattr(wl, "collective_buffer"):
+        collective = collective_alone(wl.collective_buffer(), 100, world)
 
     cpu_baseline = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload == "train_step":
-        points = 2**17
-        rate, threads, _ = cpu_training_step_rate(steps=8, warmup=1, points=points)
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and is_train:
+        rate, threads, _ = cpu_training_step_rate(steps=2, warmup=1, points=TRAIN_POINTS)
         cpu_baseline = {"value": rate, "unit": "points/s", "cores": threads, "kind": "port",
-                        "sample": f"8 steps of {points} points, float32 CPU port of the same step (oracle/)"}  # fmt: skip
+                        "sample": f"2 steps (after 1 warm-up) of {TRAIN_POINTS} points, float32 CPU port of the same step (oracle/)"}  # fmt: skip
     elif rank == 0 and world == 1 and not args.no_cpu_baseline:
         rate, threads, sample = cpu_operator_rate(args.workload)
         cpu_baseline = {"value": rate, "unit": "points/s", "cores": threads, "kind": "port", "sample": sample}
 
+    extra = wl.extra() if hasattr(wl, "extra") else {}  # may time more steps: every rank takes part
     if rank == 0:
+        config = workload_config(wl.name)
+        config["units_per_gpu_per_step"] = wl.units
+        if args.workload == "hash":
+            config["l2"] = "table (48.8 MB) is meant to stay L2 resident; no flush"
         line = {
             "metric": METRIC, "value": value, "unit": "points/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
-            "config": {"workload": wl.name, "units_per_gpu_per_step": wl.units,
-                       "l2": "per-step inputs and intermediates exceed the 126 MB L2; no explicit flush"
-                       if args.workload != "hash" else "table (48.8 MB) is meant to stay L2 resident; no flush",
-                       "timing": timing},
-            "clocks": clock_summary, "e2e": e2e, "gpu_launches": launches,
-            "roofline": roofline, "l2_probe": l2, "kernels": breakdown, "cpu_baseline": cpu_baseline,
+            "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": config, "timing": timing,
+            "step_quantiles": quantiles, "clocks": clock_summary, "e2e": e2e, "gpu_launches": launches,
+            "roofline": roofline, "roofline_l2_requests": request_roofline, "kernels": breakdown,
+            "collective_alone": collective, "cpu_baseline": cpu_baseline,
+            "last_loss": losses[0] if losses else None,
         }  # fmt: skip
-        print(json.dumps(line), flush=True)
+        line.update(extra)
+        print(json.dumps(line, allow_nan=False), flush=True)
     if world > 1:
         dist.destroy_process_group()
 

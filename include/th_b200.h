@@ -12,10 +12,18 @@
  *     until the work queued on `stream` has finished.  Pointers named *_host are read
  *     before the call returns.
  *   - every call is asynchronous on `stream` (a cudaStream_t passed as void*), never
- *     synchronises, and never allocates device memory: scratch is passed in by the
- *     caller, sized by the matching *_workspace_bytes query.
- *   - the library keeps no mutable global state besides per-device attribute caches, so
- *     it can be driven from several host threads and from one process per GPU.
+ *     synchronises (the two *_tc_status queries excepted), and never allocates device
+ *     memory: scratch is passed in by the caller, sized by the matching *_workspace_bytes
+ *     query (th_mlp_bwd_static excepted: it uses an array inside the library image, see there).
+ *   - global state of the library: per-device attribute caches behind a mutex, the launch
+ *     counter th_launch_count reads (atomic), one device-side status word per tensor-core
+ *     kernel family, and the scratch array of th_mlp_bwd_static.  Apart from that last entry
+ *     point, calls may come from several host threads and from one process per GPU.
+ *   - environment switches, read once per process, for A/B runs and for testing the
+ *     fall-back kernels: TH_MLP_LEGACY=1 sends the fused and the reversible MLP to their
+ *     mma.sync kernels, TH_MLP_NO_TMA=1 stages weights with plain loads, TH_MLP_NO_PIPE=1
+ *     disables the multi-tile tcgen05 MLP kernels, TH_MLP_SLOTS=n caps the forward's row tiles
+ *     in flight per CTA.
  *
  * dtype codes: TH_F32 = 0, TH_F16 = 1, TH_BF16 = 2.
  * activation codes: TH_ACT_NONE = 0, TH_ACT_RELU = 1, TH_ACT_SILU = 2, TH_ACT_RELU2 = 3
@@ -168,7 +176,10 @@ int64_t th_mlp_workspace_bytes(int d_in, int d_hidden, int d_out, int depth);
  * (triton_helpers/layers/fully_fused_mlp/kernel.py:599-633 -> _bwd_kernel_rfs :326-500).
  * Writes grad_x (rows, d_in) and the parameter gradients in `dtype`; any gradient pointer may be
  * null to skip it.  workspace_dev is caller-provided scratch of th_mlp_workspace_bytes() bytes;
- * the call zero-fills it, accumulates fp32 partial sums there and rounds once at the end. */
+ * the call zero-fills it, accumulates fp32 partial sums there and rounds once at the end.  When the
+ * queued work has finished the workspace still holds those fp32 sums, laid out
+ * [w_in | w_hid | w_out | b_in | b_hid | b_out] (each row-major, unpadded): a caller that wants the
+ * gradients in fp32, or normalised before they are rounded, reads them there (th_scale_cast). */
 int th_mlp_bwd(const void *x_dev, int64_t x_stride, const void *w_in_dev, const void *b_in_dev,
                const void *w_hid_dev, const void *b_hid_dev, const void *w_out_dev, const void *b_out_dev,
                const void *grad_out_dev, int64_t go_stride, void *grad_x_dev, int64_t gx_stride,
@@ -256,22 +267,16 @@ int th_mse_grad(const void *pred_dev, const void *target_dev, void *grad_dev, fl
  * with fp32 moments: g = grad * grad_scale; m, v updated; param -= lr / (1 - beta1^step) * m /
  * (sqrt(v) / sqrt(1 - beta2^step) + eps).  step counts from 1.  With zero_grad != 0 the gradient
  * buffer is cleared in the same pass (the table gradient must start at zero every step,
- * triton_helpers/layers/hash_encoding/kernel.py:636). */
+ * triton_helpers/layers/hash_encoding/kernel.py:636).  An element whose scaled gradient is not
+ * finite keeps its parameter and moments and adds one to *skipped_dev (a device int the caller
+ * zeroes and reads; may be null). */
 int th_adam_step(void *param_dev, void *grad_dev, float *exp_avg_dev, float *exp_avg_sq_dev, int64_t n_elems,
                  float lr, float beta1, float beta2, float eps, int step, float grad_scale, int zero_grad,
-                 int dtype, void *stream);
+                 int dtype, int *skipped_dev, void *stream);
 
-/* ------------------------------------------------------------------------------------------
- * Measurement aid (no counterpart in triton_helpers): reads of an L2-resident buffer in the two
- * patterns the hash encoding makes.  mode 0: coalesced 16-byte streaming reads, `iters` passes over
- * the buffer; mode 1: 4-byte reads from pseudo-random 32-byte sectors, eight in flight per thread,
- * `iters` rounds; mode 2: the same pattern with float16-pair reductions instead of reads (the buffer's
- * contents are overwritten).  *work_out_host receives the bytes read (mode 0) or the number of
- * gathers / updates (modes 1, 2) of the launch; the caller times it with CUDA events.  `sink_dev` is
- * a 4-byte device scratch word.
- * ------------------------------------------------------------------------------------------ */
-int th_probe_l2(void *buffer_dev, int64_t n_bytes, int mode, int iters, void *sink_dev, int64_t *work_out_host,
-                void *stream);
+/* dst[i] = src[i] * scale rounded to `dtype`: turns the fp32 sums th_mlp_bwd leaves in its workspace
+ * (laid out [w_in | w_hid | w_out | b_in | b_hid | b_out]) into a normalised 16-bit gradient buffer. */
+int th_scale_cast(const float *src_dev, void *dst_dev, int64_t n_elems, float scale, int dtype, void *stream);
 
 #ifdef __cplusplus
 }

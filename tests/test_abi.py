@@ -40,7 +40,7 @@ def test_every_declared_symbol_is_exported_and_bound(library):
 
 
 def test_version_and_error_text(library):
-    assert library.th_version() >= 1
+    assert library.th_version() >= 2
     assert isinstance(library.th_last_error_string(), bytes)
 
 

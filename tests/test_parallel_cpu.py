@@ -12,6 +12,7 @@ import torch.multiprocessing as mp
 from triton_helpers_b200.parallel import (
     PendingReduce,
     allreduce_gradients,
+    gradient_scales,
     init_from_env,
     level_passes,
     plan_buckets,
@@ -114,6 +115,69 @@ def _worker(rank: int, world: int, port: int, results):
         results[rank] = True
     finally:
         dist.destroy_process_group()
+
+
+def test_gradient_scales_recover_the_mean_loss_gradient():
+    # one rank, float64: the three factors undo the loss scale and the normalisation exactly
+    g = torch.Generator().manual_seed(0)
+    rows, d_out, s = 1000, 4, 1.0 / 8
+    pred, target = torch.randn(rows, d_out, generator=g, dtype=torch.float64), torch.rand(rows, d_out, generator=g, dtype=torch.float64)
+    w = torch.randn(d_out, 3, generator=g, dtype=torch.float64, requires_grad=True)
+    feats = torch.randn(rows, 3, generator=g, dtype=torch.float64)
+    ((feats @ w.T + pred - target) ** 2).mean().backward()
+    stored_sum = ((feats @ w.T + pred - target).detach() * s).T @ feats  # what a backward fed (diff * s) accumulates
+    cast, table_scale, mlp_scale = gradient_scales(rows, 1, d_out, s)
+    torch.testing.assert_close(stored_sum * cast * mlp_scale, w.grad)
+    torch.testing.assert_close(stored_sum * table_scale, w.grad)
+    # more ranks: every factor that multiplies a SUM over ranks carries 1 / world
+    assert gradient_scales(rows, 4, d_out, s)[2] == mlp_scale / 4 and gradient_scales(rows, 4, d_out, s)[0] == cast
+
+
+def _sum_worker(rank: int, world: int, port: int, results):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.set_num_threads(1)
+    init_from_env("gloo")
+    try:
+        # Per-rank float32 sums of the size the cfg 3 step produces (|dW| ~ 2e4 with 2^21 rows and loss scale
+        # 1/16).  Rounded to float16 as they are, four of them overflow; normalised first they do not.
+        rows, s, d_out = 2**21, 1.0 / 16, 16
+        g = torch.Generator().manual_seed(7)
+        shape = torch.rand(64, 64, generator=g) + 0.5            # same on every rank
+        sums = shape * 2.0e4 * (1.0 + 0.1 * rank)                # this rank's float32 workspace
+        cast, _, mlp_scale = gradient_scales(rows, world, d_out, s)
+        table = torch.full((1001, 2), float(rank + 1), dtype=torch.float16)
+        flat = torch.zeros(2016 + 64 * 64, dtype=torch.float16)  # [table | pad | MLP], as the trainer lays it out
+        flat[:2002] = table.reshape(-1)
+        flat[2016:] = (sums * cast).to(torch.float16).reshape(-1)  # what th_scale_cast writes
+        pending = PendingReduce(bucket_bytes=0)
+        pending.start([flat])
+        pending.finish()
+        got = flat[2016:].float().view(64, 64) * mlp_scale
+        want = sum(shape.double() * 2.0e4 * (1.0 + 0.1 * r) for r in range(world)) * 2.0 / (rows * world * d_out * s)
+        assert torch.isfinite(flat).all()
+        torch.testing.assert_close(got.double(), want, rtol=4e-3, atol=0)
+        assert torch.all(flat[:2002] == sum(range(1, world + 1)))
+        # the convention this replaces: unnormalised float16 sums
+        naive = sums.to(torch.float16)
+        dist.all_reduce(naive)
+        assert not torch.isfinite(naive).all()
+        results[rank] = True
+    finally:
+        dist.destroy_process_group()
+
+
+def test_four_rank_gloo_sum_of_large_gradients_in_float16():
+    world = 4
+    ctx = mp.get_context("spawn")
+    results = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_sum_worker, args=(r, world, port, results)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=180)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    assert dict(results) == {r: True for r in range(world)}
 
 
 def test_two_rank_gloo_gradient_sum():

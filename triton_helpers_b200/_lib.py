@@ -83,10 +83,10 @@ SIGNATURES = {
     "th_adam_step": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_float, c_float, c_float, c_int, c_float, c_int,
-         c_int, c_void_p],
+         c_int, c_void_p, c_void_p],
     ),
+    "th_scale_cast": (c_int, [c_void_p, c_void_p, c_int64, c_float, c_int, c_void_p]),
     "th_launch_count": (ctypes.c_longlong, []),
-    "th_probe_l2": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, _I64P, c_void_p]),
 }  # fmt: skip
 
 
@@ -99,7 +99,7 @@ class KernelTimer:
     """
 
     LAUNCHING = ("th_hash_fwd", "th_hash_bwd", "th_mlp_fwd", "th_mlp_fwd_mse", "th_mlp_bwd", "th_rev_fwd", "th_rev_bwd",
-                 "th_mse_grad", "th_adam_step")  # fmt: skip
+                 "th_mse_grad", "th_adam_step", "th_scale_cast")  # fmt: skip
 
     def __init__(self):
         self.records = []

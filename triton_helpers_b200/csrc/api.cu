@@ -31,7 +31,7 @@ int sm_count() {
 
 }  // namespace th
 
-extern "C" int th_version(void) { return 1; }
+extern "C" int th_version(void) { return 2; }
 
 extern "C" long long th_launch_count(void) { return th::launches_so_far(); }
 

@@ -203,7 +203,6 @@ mlp_fwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
     const uint32_t taddr = tmem + seat.lane_base;
     uint32_t phase = 0;
     const long long n_tiles = (n_rows + kTileRows - 1) / kTileRows;
-    TH_TRACE_BEGIN
 
     // Input tiles alternate between two buffers: while tile t runs through its layers in place in
     // buffer t & 1, tile t + 1 streams into the other one.
@@ -223,34 +222,25 @@ mlp_fwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
         const long long row0 = tile * kTileRows;
         unsigned char *act_tile = smem + cur * kTileBytes;
         const uint32_t act_addr = smem_addr(act_tile);
-        TH_STAMP(100);
         async_tile_wait();
-        TH_STAMP(101);
         fence_async_smem();
         tc_fence_before();
         __syncthreads();
-        TH_STAMP(102);
         if (abort_flag) break;
         // the other buffer is free (its tile finished before the barrier above): start the next input
         if (tile + gridDim.x < n_tiles) start_input(tile + gridDim.x, cur ^ 1);
         for (int l = 0; l <= s.depth; ++l) {
             const int in_pad = l == 0 ? s.ki : s.h;
             const int out_pad = l == s.depth ? s.no : s.h;
-            TH_STAMP(9);
             if (threadIdx.x < 32) {
                 const bool leader = elect_one();
                 tc_fence_after();
-                TH_STAMP(10);
                 issue_gemm(leader, tmem, act_addr, 32, smem_addr(weight_tile(smem, P, s, l)), 32, in_pad / 16,
                            instr_desc(128, out_pad, bf16, 0, 0), false);
-                TH_STAMP(11);
                 if (leader) mma_commit(bar);
-                TH_STAMP(12);
                 __syncwarp();
             }
-            TH_STAMP(1);
             const bool ok = cta_wait_mma(bar, phase, &abort_flag);
-            TH_STAMP(2);
             if (!ok) {
                 g_tc_status = 1;
             } else if (l < s.depth) {
@@ -260,20 +250,16 @@ mlp_fwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
                 output_epilogue<T, BIAS>(taddr, seat, out_pad, bias + l * kMaxDim, y + (live ? row0 + seat.row : 0) * y_stride,
                                          s.d_out, live, y_vec);
             }
-            TH_STAMP(3);
             if (l < s.depth) {
                 fence_async_smem();
-                TH_STAMP(4);
                 tc_fence_before();
                 __syncthreads();
-                TH_STAMP(5);
                 if (abort_flag) break;
             }
         }
         tc_fence_before();
         if (abort_flag) break;
     }
-    TH_TRACE_END;
     cta_teardown(tmem, P.tmem_cols);
 }
 
@@ -452,7 +438,6 @@ mlp_fwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
     unsigned char *buffers = smem + 2 * slot * kTileBytes;
     uint32_t acc_phase = 0;  // tracked by the issuer warp
     float loss = 0.f;        // MSE: this thread's share of sum (prediction - target)^2
-    TH_TRACE_BEGIN
 
     auto fetch_input = [&](int b, long long k) {  // by the issuer warp
         if (elect_one()) {
@@ -472,12 +457,9 @@ mlp_fwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
         const uint32_t tile_addr = smem_addr(tile);
         const uint32_t row_addr = tile_addr + row * 128, row_swizzle = (row & 7) << 4;  // chunk c of the row: row_addr + ((c << 4) ^ row_swizzle)
         if (issuer) {
-            TH_STAMP(40);
             // the other buffer's last reader was the previous tile of this slot: finished
             if (k + S < n_mine && !*reinterpret_cast<volatile int *>(&abort_flag)) fetch_input(b ^ 1, k + S);
-            TH_STAMP(41);
             pipe_wait(smem_addr(&bars.in_full[slot][b]), static_cast<uint32_t>((q >> 1) & 1), &abort_flag);
-            TH_STAMP(42);
         }
         for (int l = 0; l <= s.depth; ++l) {
             const int in_pad = l == 0 ? s.ki : s.h;
@@ -493,14 +475,11 @@ mlp_fwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
                                instr_desc(128, out_pad, bf16, 0, 0), false);
                     if (leader) mma_commit(acc_bar);
                     __syncwarp();
-                    TH_STAMP(43);
                     pipe_wait(acc_bar, acc_phase, &abort_flag);
                     acc_phase ^= 1u;
                 }
-                TH_STAMP(44);
             }
             slot_barrier(slot);
-            TH_STAMP(47);
             if (!*reinterpret_cast<volatile int *>(&abort_flag)) {
                 tc_fence_after();
                 const float *layer_bias = bias + l * kMaxDim;
@@ -533,9 +512,7 @@ mlp_fwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
                 }
                 tc_fence_before();
             }
-            TH_STAMP(45);
             slot_barrier(slot);
-            TH_STAMP(46);
         }
     }
 
@@ -546,7 +523,6 @@ mlp_fwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
     }
 
     // ---- teardown ----
-    TH_TRACE_END;
     tc_fence_before();
     __syncthreads();
     if (warp == 0)
@@ -641,7 +617,6 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
     uint32_t phase = 0;
     bool first_tile = true;
     const long long n_tiles = (n_rows + kTileRows - 1) / kTileRows;
-    TH_TRACE_BEGIN
     auto act_tile = [&](int l) { return smem + l * kTileBytes; };
     auto dw_col = [&](int l) { return kAccCols + (l == 0 ? 0 : s.ki + (l - 1) * s.h); };
 
@@ -656,7 +631,6 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
     }
     for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         const long long row0 = tile * kTileRows;
-        TH_STAMP(70);
         // ---- phase 1: recompute the forward, parking every layer input ----
         if (kPrefetch) {
             commit_tile(act_tile(0), x_next, s.ki);
@@ -670,7 +644,6 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
         fence_async_smem();
         tc_fence_before();
         __syncthreads();
-        TH_STAMP(71);
         if (abort_flag) break;
         if (kPrefetch && tile + gridDim.x < n_tiles) {
             fetch_tile<T>(x_next, x, x_stride, (tile + gridDim.x) * kTileRows, n_rows, s.d_in, s.ki, x_vec);
@@ -686,19 +659,15 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
                 if (leader) mma_commit(bar);
                 __syncwarp();
             }
-            TH_STAMP(72);
             const bool ok = cta_wait_mma(bar, phase, &abort_flag);
-            TH_STAMP(73);
             if (!ok) {
                 g_tc_status = 1;
             } else {
                 hidden_epilogue<T, ACT, false>(taddr, seat, s.h, nullptr, act_tile(l + 1));
             }
-            TH_STAMP(74);
             fence_async_smem();
             tc_fence_before();
             __syncthreads();
-            TH_STAMP(75);
             if (abort_flag) break;
         }
         if (abort_flag) break;
@@ -724,9 +693,7 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
                 if (leader) mma_commit(bar);
                 __syncwarp();
             }
-            TH_STAMP(76);
             const bool ok = cta_wait_mma(bar, phase, &abort_flag);
-            TH_STAMP(77);
             if (!ok) {
                 g_tc_status = 1;
             } else if (l > 0) {
@@ -736,11 +703,9 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
                 const bool live = row0 + seat.row < n_rows;
                 dx_epilogue<T>(taddr, seat, in_pad, gx + (live ? row0 + seat.row : 0) * gx_stride, s.d_in, live, gx_vec);
             }
-            TH_STAMP(78);
             fence_async_smem();
             tc_fence_before();
             __syncthreads();
-            TH_STAMP(79);
             if (abort_flag) break;
             buf ^= 1;
         }
@@ -748,7 +713,6 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
         first_tile = false;
     }
 
-    TH_TRACE_END;
     // ---- flush the weight gradients this CTA accumulated in TMEM ----
     if (!abort_flag && !first_tile) {
         tc_fence_after();
@@ -846,7 +810,6 @@ mlp_bwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
     auto weight_addr = [&](int l) { return smem_addr(weight_tile(smem, P, s, l)); };
     const uint32_t acc_bar = smem_addr(&bars.acc_full), ready_bar = smem_addr(&bars.ready);
     volatile int *abort_now = &abort_flag;
-    TH_TRACE_BEGIN
 
     if (warp == 8) {
         // ================= issuer =================
@@ -973,9 +936,7 @@ mlp_bwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
             auto act_addr = [&](int l) { return smem_base + static_cast<uint32_t>((base + l) % n_act) * kTileBytes; };
             // ---- phase 1 ----
             for (int l = 0; l < d; ++l) {
-                TH_STAMP(80);
                 const bool ok1 = wait_acc();
-                TH_STAMP(81);
                 if (ok1) {
                     const int n = s.h / kGroups;  // this thread's columns
                     const uint32_t dst = act_addr(l + 1) + row_off;
@@ -984,15 +945,12 @@ mlp_bwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
                         st_shared_16(dst + (((first + u) << 4) ^ row_swizzle), finish8<T, ACT, false>(piece, nullptr));
                     });
                 }
-                TH_STAMP(82);
                 publish();
             }
             // ---- phase 2 ----
             for (int l = d; l >= 0; --l) {
                 const int in_pad = l == 0 ? s.ki : s.h;
-                TH_STAMP(83);
                 const bool ok = wait_acc();
-                TH_STAMP(84);
                 const int n = in_pad / kGroups;
                 const int first = seat.group * (n / 8);
                 if (ok && l > 0) {
@@ -1017,7 +975,6 @@ mlp_bwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
                         if (live) store_chunk_to_global<T>(row_ptr, first + u, s.d_in, finish8<T, TH_ACT_NONE, false>(piece, nullptr), gx_vec);
                     });
                 }
-                TH_STAMP(85);
                 publish();
             }
             if (d > 0) {
@@ -1026,7 +983,6 @@ mlp_bwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
             }
         }
     }
-    TH_TRACE_END;
 
     // ---- flush the weight gradients this CTA accumulated in TMEM ----
     tc_fence_before();
@@ -1314,17 +1270,6 @@ int mlp_bwd_tc(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_s
 
 }  // namespace th
 
-#ifdef TH_TC_TRACE
-extern "C" int th_tc_trace_read(long long *out_host, int max_pairs) {
-    int n = 0;
-    cudaMemcpyFromSymbol(&n, th::g_trace_n, sizeof(int));
-    if (n > max_pairs) n = max_pairs;
-    cudaMemcpyFromSymbol(out_host, th::g_trace, sizeof(long long) * 2 * n);
-    int zero = 0;
-    cudaMemcpyToSymbol(th::g_trace_n, &zero, sizeof(int));
-    return n;
-}
-#endif
 
 // 1 when tensor maps can be built in this process (the driver exposes cuTensorMapEncodeTiled), i.e.
 // when the tensor-core MLP kernels load their weights by TMA; 0 when they fall back to plain loads.

@@ -76,9 +76,16 @@ struct AdamScalars {
     int zero_grad;            // write zeros back into the gradient buffer
 };
 
+// One element.  A gradient that is not finite (a 16-bit sum that overflowed, a NaN from upstream)
+// leaves the parameter and both moments as they were and is counted in `skipped`: one bad element
+// must not turn into inf / inf = NaN in the parameter and poison every later step.
 template <typename T>
-__device__ __forceinline__ T adam_one(T p, T g_in, float &m, float &v, const AdamScalars &a) {
+__device__ __forceinline__ T adam_one(T p, T g_in, float &m, float &v, const AdamScalars &a, int &skipped) {
     const float g = to_float<T>(g_in) * a.grad_scale;
+    if (!isfinite(g)) {
+        ++skipped;
+        return p;
+    }
     m = a.beta1 * m + (1.f - a.beta1) * g;
     v = a.beta2 * v + (1.f - a.beta2) * g * g;
     const float denom = sqrtf(v) / a.bias2_sqrt + a.eps;
@@ -88,7 +95,8 @@ __device__ __forceinline__ T adam_one(T p, T g_in, float &m, float &v, const Ada
 template <typename T>
 __global__ void __launch_bounds__(kOptThreads)
 adam_kernel(T *__restrict__ param, T *__restrict__ grad, float *__restrict__ exp_avg, float *__restrict__ exp_avg_sq,
-            long long n, const AdamScalars a) {
+            long long n, const AdamScalars a, int *__restrict__ skipped_total) {
+    int skipped = 0;
     const long long packets = n / 8;
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < packets;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -97,7 +105,7 @@ adam_kernel(T *__restrict__ param, T *__restrict__ grad, float *__restrict__ exp
         Vec8<float> m = reinterpret_cast<Vec8<float> *>(exp_avg)[i];
         Vec8<float> v = reinterpret_cast<Vec8<float> *>(exp_avg_sq)[i];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) p.v[k] = adam_one<T>(p.v[k], g.v[k], m.v[k], v.v[k], a);
+        for (int k = 0; k < 8; ++k) p.v[k] = adam_one<T>(p.v[k], g.v[k], m.v[k], v.v[k], a, skipped);
         reinterpret_cast<Vec8<T> *>(param)[i] = p;
         reinterpret_cast<Vec8<float> *>(exp_avg)[i] = m;
         reinterpret_cast<Vec8<float> *>(exp_avg_sq)[i] = v;
@@ -110,9 +118,20 @@ adam_kernel(T *__restrict__ param, T *__restrict__ grad, float *__restrict__ exp
     }
     for (long long i = packets * 8 + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
-        param[i] = adam_one<T>(param[i], grad[i], exp_avg[i], exp_avg_sq[i], a);
+        param[i] = adam_one<T>(param[i], grad[i], exp_avg[i], exp_avg_sq[i], a, skipped);
         if (a.zero_grad) grad[i] = from_float<T>(0.f);
     }
+    if (skipped_total && skipped) atomicAdd(skipped_total, skipped);
+}
+
+// dst[i] = round(src[i] * scale): the float32 sums a backward pass left in its workspace, normalised
+// and rounded into a 16-bit (or float32) gradient buffer.
+template <typename T>
+__global__ void __launch_bounds__(kOptThreads)
+scale_cast_kernel(const float *__restrict__ src, T *__restrict__ dst, long long n, float scale) {
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x)
+        dst[i] = from_float<T>(src[i] * scale);
 }
 
 unsigned stream_grid(long long n) {
@@ -155,7 +174,7 @@ extern "C" int th_mse_grad(const void *pred_dev, const void *target_dev, void *g
 
 extern "C" int th_adam_step(void *param_dev, void *grad_dev, float *exp_avg_dev, float *exp_avg_sq_dev, int64_t n_elems,
                             float lr, float beta1, float beta2, float eps, int step, float grad_scale, int zero_grad,
-                            int dtype, void *stream) {
+                            int dtype, int *skipped_dev, void *stream) {
     if (n_elems < 0) return fail(TH_ERR_BAD_ARG, "negative element count");
     if (step < 1) return fail(TH_ERR_BAD_ARG, "step counts from 1");
     if (n_elems == 0) return TH_OK;
@@ -169,15 +188,32 @@ extern "C" int th_adam_step(void *param_dev, void *grad_dev, float *exp_avg_dev,
     const unsigned grid = stream_grid(n_elems);
     switch (dtype) {
         case TH_F32:
-            adam_kernel<float><<<grid, kOptThreads, 0, st>>>(static_cast<float *>(param_dev), static_cast<float *>(grad_dev), exp_avg_dev, exp_avg_sq_dev, n_elems, a);
+            adam_kernel<float><<<grid, kOptThreads, 0, st>>>(static_cast<float *>(param_dev), static_cast<float *>(grad_dev), exp_avg_dev, exp_avg_sq_dev, n_elems, a, skipped_dev);
             break;
         case TH_F16:
-            adam_kernel<__half><<<grid, kOptThreads, 0, st>>>(static_cast<__half *>(param_dev), static_cast<__half *>(grad_dev), exp_avg_dev, exp_avg_sq_dev, n_elems, a);
+            adam_kernel<__half><<<grid, kOptThreads, 0, st>>>(static_cast<__half *>(param_dev), static_cast<__half *>(grad_dev), exp_avg_dev, exp_avg_sq_dev, n_elems, a, skipped_dev);
             break;
         case TH_BF16:
-            adam_kernel<__nv_bfloat16><<<grid, kOptThreads, 0, st>>>(static_cast<__nv_bfloat16 *>(param_dev), static_cast<__nv_bfloat16 *>(grad_dev), exp_avg_dev, exp_avg_sq_dev, n_elems, a);
+            adam_kernel<__nv_bfloat16><<<grid, kOptThreads, 0, st>>>(static_cast<__nv_bfloat16 *>(param_dev), static_cast<__nv_bfloat16 *>(grad_dev), exp_avg_dev, exp_avg_sq_dev, n_elems, a, skipped_dev);
             break;
         default: return fail(TH_ERR_BAD_ARG, "unknown dtype %d", dtype);
     }
     return launch_status("adam_kernel launch");
+}
+
+extern "C" int th_scale_cast(const float *src_dev, void *dst_dev, int64_t n_elems, float scale, int dtype, void *stream) {
+    if (n_elems < 0) return fail(TH_ERR_BAD_ARG, "negative element count");
+    if (n_elems == 0) return TH_OK;
+    if (!src_dev || !dst_dev) return fail(TH_ERR_BAD_ARG, "null tensor pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const long long blocks = (n_elems + kOptThreads - 1) / kOptThreads;
+    const long long cap = static_cast<long long>(sm_count()) * 8;
+    const unsigned grid = static_cast<unsigned>(blocks < cap ? blocks : cap);
+    switch (dtype) {
+        case TH_F32: scale_cast_kernel<float><<<grid, kOptThreads, 0, st>>>(src_dev, static_cast<float *>(dst_dev), n_elems, scale); break;
+        case TH_F16: scale_cast_kernel<__half><<<grid, kOptThreads, 0, st>>>(src_dev, static_cast<__half *>(dst_dev), n_elems, scale); break;
+        case TH_BF16: scale_cast_kernel<__nv_bfloat16><<<grid, kOptThreads, 0, st>>>(src_dev, static_cast<__nv_bfloat16 *>(dst_dev), n_elems, scale); break;
+        default: return fail(TH_ERR_BAD_ARG, "unknown dtype %d", dtype);
+    }
+    return launch_status("scale_cast_kernel launch");
 }

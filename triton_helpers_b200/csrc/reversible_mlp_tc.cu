@@ -352,7 +352,6 @@ rev_bwd_tc_kernel(const RevShape s, const RevParams p, const __grid_constant__ R
             pending_dw1 = pending_dw2 = nullptr;
         }
     };
-    TH_TRACE_BEGIN
     float *cta_acc = workspace + static_cast<size_t>(blockIdx.x) * rev_cta_floats(s);
     // instruction descriptors: forward-type, dgrad (B MN-major), reconstruction (A negated), wgrad (both MN-major, M = 64)
     const uint32_t id_z = instr_desc(128, s.hid, bf16, 0, 0);
@@ -395,7 +394,6 @@ rev_bwd_tc_kernel(const RevShape s, const RevParams p, const __grid_constant__ R
                 const uint32_t w1 = smem_addr(w + m1 * kWTileBytes), w2 = smem_addr(w + m2 * kWTileBytes);
                 const uint32_t out_col = pass == 0 ? kS2 : kS1, in_d_col = pass == 0 ? kD1 : kD2;
                 bool leader = false;
-                TH_STAMP(90);
                 // step A: z = U . W1^T and dh = DY . W2 together
                 if (threadIdx.x < 32) {
                     leader = elect_one();
@@ -405,10 +403,8 @@ rev_bwd_tc_kernel(const RevShape s, const RevParams p, const __grid_constant__ R
                     if (leader) mma_commit(bar);
                     __syncwarp();
                 }
-                TH_STAMP(91);
                 flush_pending();  // the previous pass's weight gradients, while the GEMMs above run
                 cta_wait_mma(bar, phase, &abort_flag);
-                TH_STAMP(92);
                 {
                     // h = act(z) first (also the ReLU mask), then dz = dh where h > 0
                     const int n = s.hid / kGroups, first = seat.group * (n / 8);
@@ -430,9 +426,7 @@ rev_bwd_tc_kernel(const RevShape s, const RevParams p, const __grid_constant__ R
                         st_shared_16(dz_row + off, g);
                     });
                 }
-                TH_STAMP(93);
                 publish_tiles();
-                TH_STAMP(94);
                 // step B: undo the branch, push the gradient through, form both weight gradients
                 if (threadIdx.x < 32) {
                     leader = elect_one();
@@ -442,22 +436,17 @@ rev_bwd_tc_kernel(const RevShape s, const RevParams p, const __grid_constant__ R
                     issue_gemm(leader, tmem + kDW2, smem_addr(dy_tile), 2048, smem_addr(h_tile), 2048, kTileRows / 16, id_dw2, false);
                     issue_gemm(leader, tmem + kDW1, smem_addr(dz_tile), 2048, smem_addr(u_tile), 2048, kTileRows / 16, id_dw1, false);
                 }
-                TH_STAMP(95);
                 commit_and_wait(leader, bar, phase, &abort_flag);
-                TH_STAMP(96);
                 // next pass: its input is the stream just reconstructed, its output gradient the one just updated
                 stream_epilogue<T, false>(taddr + out_col, seat, s.half, nullptr, u_tile, nullptr, false);
                 stream_epilogue<T, false>(taddr + in_d_col, seat, s.half, nullptr, dy_tile, nullptr, false);
-                TH_STAMP(97);
                 pending_dw1 = block_acc + m1 * kMatFloats;
                 pending_dw2 = block_acc + m2 * kMatFloats;
-                TH_STAMP(98);
                 if (pass == 1) {  // next block's weights have landed
                     if (!use_tma) async_tile_wait();
                     else if (more) ring_wait(ring_bars, step + 1, &abort_flag);
                 }
                 publish_tiles();
-                TH_STAMP(99);
             }
         }
         // the stream is now the reconstructed input, the gradient stream the input gradient
@@ -476,7 +465,6 @@ rev_bwd_tc_kernel(const RevShape s, const RevParams p, const __grid_constant__ R
             __syncthreads();
         }
     }
-    TH_TRACE_END;
     if (!abort_flag) {
         tc_fence_after();
         flush_pending();
@@ -643,14 +631,3 @@ extern "C" int th_rev_tc_status(void) {
     return status;
 }
 
-#ifdef TH_TC_TRACE
-extern "C" int th_rev_trace_read(long long *out_host, int max_pairs) {
-    int n = 0;
-    cudaMemcpyFromSymbol(&n, th::g_trace_n, sizeof(int));
-    if (n > max_pairs) n = max_pairs;
-    cudaMemcpyFromSymbol(out_host, th::g_trace, sizeof(long long) * 2 * n);
-    int zero = 0;
-    cudaMemcpyToSymbol(th::g_trace_n, &zero, sizeof(int));
-    return n;
-}
-#endif

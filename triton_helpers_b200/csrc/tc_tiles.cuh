@@ -35,32 +35,6 @@ constexpr int kWaitPolls = 1 << 20;
 
 __device__ int g_tc_status = 0;  // 0 = fine, 1 = an mbarrier wait ran out
 
-#ifdef TH_TC_TRACE
-// Development aid: cycle stamps of CTA 0 / thread 0 (never compiled into the shipped library).
-__device__ long long g_trace[4096];
-__device__ int g_trace_n = 0;
-#define TH_TRACE_BEGIN int trace_i = 0;
-#ifndef TH_TRACE_THREAD
-#define TH_TRACE_THREAD 0
-#endif
-#define TH_STAMP(tag)                                                             \
-    do {                                                                          \
-        if (blockIdx.x == 0 && threadIdx.x == TH_TRACE_THREAD && trace_i < 2047) { \
-            g_trace[2 * trace_i] = (tag);                                         \
-            g_trace[2 * trace_i + 1] = clock64();                                 \
-            ++trace_i;                                                            \
-        }                                                                         \
-    } while (0)
-#define TH_TRACE_END                                                              \
-    do {                                                                          \
-        if (blockIdx.x == 0 && threadIdx.x == TH_TRACE_THREAD) g_trace_n = trace_i; \
-    } while (0)
-#else
-#define TH_TRACE_BEGIN
-#define TH_TRACE_END do { } while (0)
-#define TH_STAMP(tag) do { } while (0)
-#endif
-
 // ---- PTX wrappers ------------------------------------------------------------------------------
 
 // Shared-memory matrix descriptor = {low word, high word}.  High word (constant for every tile here):

@@ -93,6 +93,22 @@ def allreduce_gradients(
                 offset += m.numel()
 
 
+def gradient_scales(rows: int, world_size: int, d_out: int, grad_out_scale: float) -> Tuple[float, float, float]:
+    r"""The three factors that tie the flat 16-bit gradient buffer of a data-parallel step to the true
+    gradient of ``mean((pred - target)^2)`` over the global batch of ``rows * world_size`` points with
+    ``d_out`` values each, when the backward pass was fed ``(pred - target) * grad_out_scale``:
+
+    * ``cast_scale``: multiplies the float32 sums over the local rows that the MLP backward leaves in its
+      workspace before they are rounded to 16 bits - ``1 / (rows * grad_out_scale)``, i.e. the buffer holds
+      the mean of the unscaled gradient.  Sums over 2^21 rows reach 1e4..1e5 and would overflow float16
+      once four ranks are added up; means of any number of rows stay of order one.
+    * ``table_adam_scale``: multiplies the summed table gradient (which holds ``grad_out_scale * sum``).
+    * ``mlp_adam_scale``: multiplies the summed MLP gradient (a sum of per-rank means).
+    """
+    per_value = 2.0 / (world_size * d_out)
+    return 1.0 / (rows * grad_out_scale), per_value / (rows * grad_out_scale), per_value
+
+
 def level_passes(level_rows: Sequence[int], n_passes: int, align: int = 4) -> List[Tuple[int, int]]:
     r"""Cuts levels ``0 .. len(level_rows)`` into at most ``n_passes`` consecutive ranges holding about
     equal numbers of table rows, with boundaries at multiples of ``align`` levels (the backward kernel
