@@ -178,7 +178,7 @@ class TrainStep:
             enc.embeddings.uniform_(-1e-4, 1e-4)
         mlp = FullyFusedMLP(32, 64, 16, depth=2, bias=False)
         self.trainer = NeuralFieldTrainer(enc.to(device).half(), mlp.to(device).half(), lr=1e-2, betas=(0.9, 0.99), eps=1e-15,
-                                          backward_passes=args.backward_passes)
+                                          backward_passes=args.backward_passes, fused=False if args.unfused else None)
         gen = torch.Generator(device=device).manual_seed(1234 + rank)  # a different batch per rank
         self.coords = torch.rand(points, 3, device=device, generator=gen)
         self.targets = torch.rand(points, 16, device=device, generator=gen).half()

@@ -112,10 +112,15 @@ int th_hash_bwd(const void *coords_dev, int64_t coord_stride_n, int64_t coord_st
                 const int32_t *level_res_host, const int64_t *level_rows_host, const int64_t *level_offset_host,
                 const int64_t *primes_host, float scale, int level_begin, int level_end, void *stream);
 
+/* Device-side status word of the encoding kernels: 0 = fine, 1 = a shared-memory accumulation of the
+ * backward pass (compare-and-swap loop, bounded) gave up and dropped an update.  Synchronises the device.
+ * No counterpart in the reference. */
+int th_hash_status(void);
+
 /*
  * Test hook for the bit-exact index check: the row index (relative to its level) and the
- * interpolation weight of every corner, computed by the same device functions the two
- * kernels above use.  Stands in for the reference's ad-hoc test kernels around
+ * interpolation weight of every corner, computed the way the two kernels above compute them: two
+ * lanes per point, each calling the kernels' own per-side index and weight functions.  Stands in for the reference's ad-hoc test kernels around
  * embedding_lookup / get_interpolation_weights
  * (tests/test_layers/test_hash_encoding.py:176-215 of the reference).
  *
@@ -159,9 +164,9 @@ int th_mlp_fwd_mse(const void *x_dev, int64_t x_stride, const void *w_in_dev, co
                    int64_t grad_stride, float *loss_sum_dev, float grad_scale, int64_t rows, int d_in, int d_hidden,
                    int d_out, int depth, int activation, int dtype, void *stream);
 
-/* Device-side status word of the tensor-core MLP kernels: 0 = fine, 1 = one of their bounded waits
- * ran out (the kernel then returned early and its results are invalid).  Synchronises the device.
- * No counterpart in the reference. */
+/* Device-side status word of the tensor-core MLP kernels (th_mlp_*, th_field_*): 0 = fine, non-zero =
+ * one of their bounded waits ran out (the kernel then returned early and its results are invalid).
+ * Synchronises the device.  No counterpart in the reference. */
 int th_mlp_tc_status(void);
 
 /* 1 when the tensor-core MLP kernels can load their weights by TMA in this process (the driver
@@ -250,6 +255,53 @@ int th_rev_bwd(const void *y_dev, int64_t y_stride, const void *w_f1_dev, const 
                void *grad_b_f2_dev, void *grad_b_g1_dev, void *grad_b_g2_dev, void *workspace_dev,
                int64_t workspace_bytes, int64_t rows, int d_model, int d_hidden, int blocks, int activation,
                int dtype, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Hash encoding and fused MLP in one kernel per direction.  NO ENTRY POINT OF THE REFERENCE
+ * CORRESPONDS: triton_helpers launches the two layers separately, and only remarks that the encoding
+ * "will be used with a fully fused MLP" with its L * F output columns staying on chip
+ * (triton_helpers/layers/hash_encoding/kernel.py:241-243).  Semantics are those of th_hash_fwd followed
+ * by th_mlp_fwd / th_mlp_fwd_mse, and of th_mlp_bwd followed by th_hash_bwd, with the MLP's input
+ * width d_in = n_levels * n_feats.  Table, weights, features and gradients share one 16-bit `dtype`.
+ * Covered: n_dims 2 or 3, n_feats 2 or 4, n_levels * n_feats a multiple of 16 up to 64, ReLU or no
+ * activation, 16-byte aligned rows; biases in the forward only.  Anything else returns
+ * TH_ERR_UNSUPPORTED and the caller runs the separate entry points.
+ * ------------------------------------------------------------------------------------------ */
+
+/* Forward.  The encoding of a 128-point tile is written straight into the first GEMM's operand tile.
+ *   feats_out_dev   (n_points, n_levels * n_feats), row stride feats_stride: the encoding, written only
+ *                   when not null (th_field_bwd needs it)
+ *   out_dev         (n_points, d_out) prediction, may be null when a target is given
+ *   target_dev      when not null: grad_dev[r, c] = (prediction - target) * grad_scale (prediction rounded
+ *                   to `dtype` first) and sum (prediction - target)^2 is added to *loss_sum_dev (fp32,
+ *                   caller-zeroed, may be null), as th_mlp_fwd_mse does */
+int th_field_fwd(const void *coords_dev, int64_t coord_stride_n, int64_t coord_stride_d, int coord_dtype,
+                 const void *table_dev, int n_dims, int n_feats, int n_levels, const int32_t *level_res_host,
+                 const int64_t *level_rows_host, const int64_t *level_offset_host, const int64_t *primes_host,
+                 float scale, const void *w_in_dev, const void *b_in_dev, const void *w_hid_dev,
+                 const void *b_hid_dev, const void *w_out_dev, const void *b_out_dev, int d_hidden, int d_out,
+                 int depth, int activation, void *feats_out_dev, int64_t feats_stride, void *out_dev,
+                 int64_t out_stride, const void *target_dev, int64_t target_stride, void *grad_dev,
+                 int64_t grad_stride, float *loss_sum_dev, float grad_scale, int64_t n_points, int dtype,
+                 void *stream);
+
+/* Bytes of fp32 scratch th_field_bwd needs: th_mlp_workspace_bytes of the same network. */
+int64_t th_field_workspace_bytes(int n_levels, int n_feats, int d_hidden, int d_out, int depth);
+
+/* Backward (bias-free networks).  From the encoding th_field_fwd wrote (feats_dev) and the gradient of
+ * the MLP's output it recomputes the activations, forms the weight gradients (fp32 sums in
+ * workspace_dev, laid out like th_mlp_bwd's: [w_in | w_hid | w_out]; the call zero-fills it first) and
+ * the gradient of the encoding, which never leaves the SM: each tile's rows are scattered into
+ * grad_table_dev (same shape and dtype as the table; the caller zero-fills it, as for th_hash_bwd).
+ * grad_feats_dev, when not null, also receives the (n_points, n_levels * n_feats) feature gradient. */
+int th_field_bwd(const void *coords_dev, int64_t coord_stride_n, int64_t coord_stride_d, int coord_dtype,
+                 int n_dims, int n_feats, int n_levels, const int32_t *level_res_host,
+                 const int64_t *level_rows_host, const int64_t *level_offset_host, const int64_t *primes_host,
+                 float scale, const void *w_in_dev, const void *w_hid_dev, const void *w_out_dev, int d_hidden,
+                 int d_out, int depth, int activation, const void *feats_dev, int64_t feats_stride,
+                 const void *grad_out_dev, int64_t go_stride, void *grad_table_dev, void *grad_feats_dev,
+                 int64_t gf_stride, void *workspace_dev, int64_t workspace_bytes, int64_t n_points, int dtype,
+                 void *stream);
 
 /* ------------------------------------------------------------------------------------------
  * Element-wise steps of a training step around the fused operators.  NO COUNTERPART IN THE

@@ -42,6 +42,21 @@ SIGNATURES = {
         [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, _I32P, _I64P, _I64P,
          c_float, c_void_p],
     ),
+    "th_hash_status": (c_int, []),
+    "th_field_fwd": (
+        c_int,
+        [c_void_p, c_int64, c_int64, c_int, c_void_p, c_int, c_int, c_int, _I32P, _I64P, _I64P, _I64P, c_float,
+         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+         c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_float, c_int64, c_int,
+         c_void_p],
+    ),
+    "th_field_workspace_bytes": (c_int64, [c_int, c_int, c_int, c_int, c_int]),
+    "th_field_bwd": (
+        c_int,
+        [c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int, _I32P, _I64P, _I64P, _I64P, c_float,
+         c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
+         c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int, c_void_p],
+    ),
     "th_mlp_fwd": (
         c_int,
         [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
@@ -98,7 +113,7 @@ class KernelTimer:
     queued.  ``summary()`` synchronises and returns ``{entry point: (calls, total ms)}``.
     """
 
-    LAUNCHING = ("th_hash_fwd", "th_hash_bwd", "th_mlp_fwd", "th_mlp_fwd_mse", "th_mlp_bwd", "th_rev_fwd", "th_rev_bwd",
+    LAUNCHING = ("th_field_fwd", "th_field_bwd", "th_hash_fwd", "th_hash_bwd", "th_mlp_fwd", "th_mlp_fwd_mse", "th_mlp_bwd", "th_rev_fwd", "th_rev_bwd",
                  "th_mse_grad", "th_adam_step", "th_scale_cast")  # fmt: skip
 
     def __init__(self):

@@ -6,9 +6,10 @@ the drop-in ``HashEncoding`` and ``FullyFusedMLP`` modules.
 
 Two ways through the step:
 
-* **direct** (table and MLP share one 16-bit dtype): the trainer calls the C ABI itself -
-  ``th_hash_fwd``, ``th_mlp_fwd_mse``, ``th_mlp_bwd``, ``th_scale_cast``, ``th_hash_bwd``,
-  ``th_adam_step`` - on buffers it keeps from step to step.  All gradients live in ONE flat 16-bit
+* **direct** (table and MLP share one 16-bit dtype): the trainer calls the C ABI itself on buffers it
+  keeps from step to step - by default the fused pair ``th_field_fwd`` (encoding + MLP + loss) and
+  ``th_field_bwd`` (MLP backward + encoding backward), else ``th_hash_fwd``, ``th_mlp_fwd_mse``,
+  ``th_mlp_bwd``, ``th_hash_bwd``; then ``th_scale_cast`` and ``th_adam_step``.  All gradients live in ONE flat 16-bit
   buffer ``[table gradient | MLP gradients]`` so that a step costs one all-reduce:
 
   - the table part holds ``grad_out_scale * sum over the local batch`` (the encoding backward adds
@@ -36,6 +37,7 @@ from . import _lib
 from .layers.fully_fused_mlp import FullyFusedMLP
 from .layers.hash_encoding import HashEncoding
 from .layers.hash_encoding.kernel import _Launch
+from .layers.neural_field.kernel import FieldUnsupported, field_backward, field_forward
 from .optim import FusedAdam, adam_update
 from .parallel import PendingReduce, allreduce_gradients, gradient_scales, level_passes
 
@@ -85,6 +87,10 @@ class NeuralFieldTrainer(nn.Module):
             overflow; Adam undoes the scale exactly.  ``None``: ``default_grad_out_scale`` of the
             global batch of the first step.
         group: process group for data parallelism (``None``: the default group, if initialised).
+        fused: direct mode only.  ``None`` (default): use the kernels that fuse the encoding with the MLP
+            when they cover the configuration, the separate operators otherwise; ``False``: always the
+            separate operators; ``True``: raise if the fused kernels do not cover the configuration.
+            ``backward_passes`` implies the separate operators.
         backward_passes: ``None`` (default): one encoding backward, then one gradient sum over the
             ranks.  An integer n (direct mode): the encoding backward runs in n level ranges, finest
             first; the gradient rows of a finished range are summed over the ranks (NCCL,
@@ -104,8 +110,10 @@ class NeuralFieldTrainer(nn.Module):
         grad_out_scale: Optional[float] = None,
         group: Optional[dist.ProcessGroup] = None,
         backward_passes: Optional[int] = None,
+        fused: Optional[bool] = None,
     ):
         super().__init__()
+        self.fused = fused
         self.encoding = encoding
         self.mlp = mlp
         self.grad_out_scale = grad_out_scale
@@ -179,44 +187,65 @@ class NeuralFieldTrainer(nn.Module):
         code, act = _lib.dtype_code(st.flat_grad), _lib.ACTIVATION_CODE[mlp.activation]
         mlp_ptrs = (st.w_in.data_ptr(), _lib.ptr(st.b_in), _lib.ptr(st.w_hid), _lib.ptr(st.b_hid), st.w_out.data_ptr(), _lib.ptr(st.b_out))
         dims = (st.d_feat, st.d_hidden, st.d_out, st.depth)
+        use_fused = self.fused is not False and not self.backward_passes
+        if use_fused and st.b_in is not None:  # the fused backward is built for bias-free networks
+            if self.fused:
+                raise FieldUnsupported("bias-free networks only (backward)")
+            use_fused = False
         with torch.cuda.device(device):
             stream = _lib.stream_ptr(device)
             st.loss_sum.zero_()
             geometry = (launch.n, d_coord, st.n_feats, enc.num_levels, launch.res, launch.rows, launch.offsets, launch.primes, launch.scale)
-            _lib.check(
-                lib.th_hash_fwd(*launch.coord_args, enc.embeddings.data_ptr(), code, st.feats.data_ptr(), st.d_feat,
-                                *geometry, 0, enc.num_levels, stream),
-                "th_hash_fwd",
-            )  # fmt: skip
-            rc = lib.th_mlp_fwd_mse(
-                st.feats.data_ptr(), st.d_feat, *mlp_ptrs, None, st.d_out, targets.data_ptr(), targets.stride(0),
-                st.grad_pred.data_ptr(), st.d_out, st.loss_sum.data_ptr(), scale, n, *dims, act, code, stream,
-            )  # fmt: skip
-            if rc == _lib.TH_ERR_UNSUPPORTED:  # shapes the fused forward + loss does not take: the two kernels it stands for
-                _lib.check(lib.th_mlp_fwd(st.feats.data_ptr(), st.d_feat, *mlp_ptrs, st.pred.data_ptr(), st.d_out, n, *dims, act, code, 0, stream), "th_mlp_fwd")
-                t = targets.contiguous()
-                _lib.check(lib.th_mse_grad(st.pred.data_ptr(), t.data_ptr(), st.grad_pred.data_ptr(), st.loss_sum.data_ptr(), n * st.d_out, scale, code, stream), "th_mse_grad")
-            else:
-                _lib.check(rc, "th_mlp_fwd_mse")
-            _lib.check(
-                lib.th_mlp_bwd(st.feats.data_ptr(), st.d_feat, *mlp_ptrs, st.grad_pred.data_ptr(), st.d_out, st.grad_feats.data_ptr(),
-                               st.d_feat, None, None, None, None, None, None, st.workspace.data_ptr(), st.workspace.numel() * 4,
-                               n, *dims, act, code, 0, stream),
-                "th_mlp_bwd",
-            )  # fmt: skip
+            weights = (st.w_in, st.w_out, st.w_hid)
+            if use_fused:
+                try:
+                    field_forward(launch, enc.embeddings.data, *weights, mlp.activation, enc.num_levels, feats_out=st.feats,
+                                  target=targets, grad_out=st.grad_pred, loss_sum=st.loss_sum, grad_scale=scale,
+                                  biases=(st.b_in, st.b_hid, st.b_out))  # fmt: skip
+                    field_backward(launch, st.feats, st.grad_pred, *weights, mlp.activation, enc.num_levels, st.table_grad, st.workspace)
+                except FieldUnsupported:
+                    if self.fused:
+                        raise
+                    self.fused = use_fused = False  # take the separate operators from now on
+                    st.loss_sum.zero_()
+            if not use_fused:
+                _lib.check(
+                    lib.th_hash_fwd(*launch.coord_args, enc.embeddings.data_ptr(), code, st.feats.data_ptr(), st.d_feat,
+                                    *geometry, 0, enc.num_levels, stream),
+                    "th_hash_fwd",
+                )  # fmt: skip
+                rc = lib.th_mlp_fwd_mse(
+                    st.feats.data_ptr(), st.d_feat, *mlp_ptrs, None, st.d_out, targets.data_ptr(), targets.stride(0),
+                    st.grad_pred.data_ptr(), st.d_out, st.loss_sum.data_ptr(), scale, n, *dims, act, code, stream,
+                )  # fmt: skip
+                if rc == _lib.TH_ERR_UNSUPPORTED:  # shapes the fused forward + loss does not take: the two kernels it stands for
+                    _lib.check(lib.th_mlp_fwd(st.feats.data_ptr(), st.d_feat, *mlp_ptrs, st.pred.data_ptr(), st.d_out, n, *dims, act, code, 0, stream), "th_mlp_fwd")
+                    t = targets.contiguous()
+                    _lib.check(lib.th_mse_grad(st.pred.data_ptr(), t.data_ptr(), st.grad_pred.data_ptr(), st.loss_sum.data_ptr(), n * st.d_out, scale, code, stream), "th_mse_grad")
+                else:
+                    _lib.check(rc, "th_mlp_fwd_mse")
+                _lib.check(
+                    lib.th_mlp_bwd(st.feats.data_ptr(), st.d_feat, *mlp_ptrs, st.grad_pred.data_ptr(), st.d_out, st.grad_feats.data_ptr(),
+                                   st.d_feat, None, None, None, None, None, None, st.workspace.data_ptr(), st.workspace.numel() * 4,
+                                   n, *dims, act, code, 0, stream),
+                    "th_mlp_bwd",
+                )  # fmt: skip
             # float32 sums over this rank's rows -> mean of the unscaled gradient, rounded into the flat buffer's tail
             _lib.check(lib.th_scale_cast(st.workspace.data_ptr(), st.mlp_grad.data_ptr(), st.mlp_grad.numel(), cast_scale, code, stream), "th_scale_cast")
             pending = PendingReduce(self.group, bucket_bytes=0)
-            passes = [(0, enc.num_levels)] if not self.backward_passes else level_passes(launch.geo.rows, self.backward_passes)
-            for i, (begin, end) in enumerate(passes):  # finest first
-                _lib.check(
-                    lib.th_hash_bwd(*launch.coord_args, st.grad_feats.data_ptr(), st.d_feat, st.table_grad.data_ptr(), code,
-                                    *geometry, begin, end, stream),
-                    "th_hash_bwd",
-                )  # fmt: skip
-                first = launch.geo.offsets[begin] * st.n_feats
-                last = st.flat_grad.numel() if i == 0 else (launch.geo.offsets[end - 1] + launch.geo.rows[end - 1]) * st.n_feats
-                pending.start([st.flat_grad[first:last]])  # one collective per range; the first carries the MLP gradients
+            if use_fused:
+                pending.start([st.flat_grad])
+            else:
+                passes = [(0, enc.num_levels)] if not self.backward_passes else level_passes(launch.geo.rows, self.backward_passes)
+                for i, (begin, end) in enumerate(passes):  # finest first
+                    _lib.check(
+                        lib.th_hash_bwd(*launch.coord_args, st.grad_feats.data_ptr(), st.d_feat, st.table_grad.data_ptr(), code,
+                                        *geometry, begin, end, stream),
+                        "th_hash_bwd",
+                    )  # fmt: skip
+                    first = launch.geo.offsets[begin] * st.n_feats
+                    last = st.flat_grad.numel() if i == 0 else (launch.geo.offsets[end - 1] + launch.geo.rows[end - 1]) * st.n_feats
+                    pending.start([st.flat_grad[first:last]])  # one collective per range; the first carries the MLP gradients
             pending.finish()
         adam_update(enc.embeddings.data.view(-1), st.table_grad.view(-1), st.table_m, st.table_v, self._steps, self.lr, self.betas,
                     self.eps, table_adam_scale, True, st.skipped)  # fmt: skip
