@@ -59,11 +59,16 @@ __device__ __forceinline__ int bar_full(int r) { return 1 + r; }
 __device__ __forceinline__ int bar_empty(int r) { return 1 + kRing + r; }
 __device__ __forceinline__ int bar_rows(int g) { return 1 + 2 * kRing + g; }
 
-// Register budget per role.  The CTA is launched with 64 registers for each of its 1024 threads; the point
-// units (6 warpgroups) give 8 each back and the row groups (2 warpgroups, whose epilogues hold 32 accumulator
-// columns at a time) take 24 more: 768 x 56 + 256 x 88 = 65 536.
-__device__ __forceinline__ void regs_for_point_unit() { asm volatile("setmaxnreg.dec.sync.aligned.u32 56;" ::: "memory"); }
-__device__ __forceinline__ void regs_for_row_group() { asm volatile("setmaxnreg.inc.sync.aligned.u32 88;" ::: "memory"); }
+// Register budget per role (setmaxnreg moves registers between warpgroups of a running CTA).
+//   backward: 1024 threads launched with 64 registers each; the point units (6 warpgroups) give 8 each back and
+//             the two row groups, whose epilogues hold 32 accumulator columns at a time, take 24 more:
+//             768 x 56 + 256 x 88 = 65 536.
+//   forward:  the gathers keep two bursts of 16 rows in flight per lane and want 72 registers, so the forward runs
+//             ONE row group: 896 threads with 72 registers each, no rebalancing.
+template <int REGS>
+__device__ __forceinline__ void regs_give_back() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS) : "memory"); }
+template <int REGS>
+__device__ __forceinline__ void regs_take() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS) : "memory"); }
 
 __device__ __forceinline__ void named_barrier(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
@@ -88,6 +93,19 @@ __device__ __forceinline__ bool rows_wait_mma(uint32_t mbar, uint32_t &phase, vo
     named_barrier(barrier_id, kRowThreads);
     tc_fence_after();
     return *abort_flag == 0;
+}
+
+// One accumulator row (out_pad a multiple of 16 columns) -> bias, activation, rounding -> 16-byte chunks handed
+// to `sink(chunk index, packed values)`, 16 columns per TMEM load: half the registers of the 32-column form.
+template <typename T, int ACT, bool BIAS, typename Sink>
+__device__ __forceinline__ void drain_row16(uint32_t taddr, int out_pad, const float *bias, Sink sink) {
+    for (int first = 0; first < out_pad; first += 16) {
+        uint32_t raw[32];
+        tmem_ld16(taddr + first, raw);
+        tmem_ld_wait();
+#pragma unroll
+        for (int u = 0; u < 2; ++u) sink(first / 8 + u, finish8<T, ACT, BIAS>(raw + 8 * u, bias + first + 8 * u));
+    }
 }
 
 // Set-up shared by both kernels: barriers, TMEM allocation by warp 0, publication.
@@ -126,8 +144,11 @@ __device__ __forceinline__ void field_teardown(uint32_t tmem, uint32_t tmem_cols
 // pass).  Row groups consume: the layers run in place in the ring buffer, the last epilogue writes the
 // prediction or (prediction - target) * scale and sums the squared error.
 
+constexpr int kFwdRowGroups = 1;
+constexpr int kFwdThreads = kUnits * kUnitThreads + kFwdRowGroups * kRowThreads;
+
 template <typename T, int D, int F, int ACT, bool BIAS>
-__global__ void __launch_bounds__(kFieldThreads, 1)
+__global__ void __launch_bounds__(kFwdThreads, 1)
 field_fwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, const T *__restrict__ table, const int n_levels,
                  const MlpShape s, const MlpParams p, const __grid_constant__ WeightMaps maps, const int use_tma,
                  T *__restrict__ feats, const long long feats_stride, T *__restrict__ y, const long long y_stride,
@@ -142,15 +163,15 @@ field_fwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, cons
     __shared__ int abort_flag;
     const TcPlan PL = tc_plan(s, false, kRing);  // kRing operand tiles, then weights and biases
     constexpr int bf16 = std::is_same<T, __half>::value ? 0 : 1;
-    constexpr uint32_t kTmemCols = 128;          // 64 accumulator columns per row group
+    constexpr uint32_t kTmemCols = 64 * kFwdRowGroups;  // 64 accumulator columns per row group (a power of two >= 32)
     volatile int *abort_now = &abort_flag;
 
     if (threadIdx.x == 0) abort_flag = 0;
     // tiles start as zeros: feature columns a narrow encoding never writes are read by the first GEMM as zeros
-    for (int e = threadIdx.x; e < kRing * kTileBytes / 16; e += kFieldThreads) reinterpret_cast<uint4 *>(smem)[e] = make_uint4(0, 0, 0, 0);
+    for (int e = threadIdx.x; e < kRing * kTileBytes / 16; e += kFwdThreads) reinterpret_cast<uint4 *>(smem)[e] = make_uint4(0, 0, 0, 0);
     {
         float *bias = reinterpret_cast<float *>(smem + PL.bias_offset);
-        for (int e = threadIdx.x; e < (s.depth + 1) * kMaxDim; e += kFieldThreads) {
+        for (int e = threadIdx.x; e < (s.depth + 1) * kMaxDim; e += kFwdThreads) {
             const int layer = e / kMaxDim, c = e % kMaxDim;
             float v = 0.f;
             if (BIAS) {
@@ -180,7 +201,6 @@ field_fwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, cons
 
     if (threadIdx.x < kUnits * kUnitThreads) {
         // ================= point unit: encoding of a tile into its ring buffer =================
-        regs_for_point_unit();
         const int unit = threadIdx.x / kUnitThreads, v = threadIdx.x % kUnitThreads;
         const int lp = v >> 1, side = v & 1;
         const uint32_t row_off = lp * 128, swz = (lp & 7) << 4;
@@ -200,17 +220,18 @@ field_fwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, cons
             if (!*abort_now) {
                 const uint32_t my_row = smem_addr(smem + r * kTileBytes) + row_off;
                 T *feat_row = feats && live ? feats + pt * feats_stride : nullptr;
-                for (int lg = 0; lg < n_levels; lg += LG) {
-                    // gathered rows stay packed (F 16-bit values in F / 2 registers) until they are used
-                    uint32_t e[LG][kSide][F / 2];
-                    float w[LG][kSide];
+                // Two chunks of gathers are in flight per lane: the loads of chunk c + 1 are issued before chunk c is
+                // used.  A warp that waits for one burst of 16 rows at a time leaves the request path idle unless 32
+                // such warps share the SM; with two bursts in flight the 24 warps of the point units keep it busy.
+                // Gathered rows stay packed (F 16-bit values in F / 2 registers) until they are used, and the
+                // interpolation weights are worked out when a chunk is used rather than kept across the loads.
+                auto issue = [&](int lg, uint32_t(&e)[LG][kSide][F / 2]) {
 #pragma unroll
-                    for (int j = 0; j < LG; ++j) {  // every gather of the chunk is issued before the first use
+                    for (int j = 0; j < LG; ++j) {
                         const int level = lg + j;
                         uint32_t cell[D], idx[kSide];
                         float t[D];
                         locate<D>(x, P.res[level], cell, t);
-                        side_weights<D>(t, side, w[j]);
                         side_indices<D>(cell, P, level, side, idx);
                         const T *base = table + P.offset[level] * F;
 #pragma unroll
@@ -225,9 +246,15 @@ field_fwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, cons
                             }
                         }
                     }
+                };
+                auto consume = [&](int lg, const uint32_t(&e)[LG][kSide][F / 2]) {
                     float acc[kChunkFeats];
 #pragma unroll
                     for (int j = 0; j < LG; ++j) {
+                        uint32_t cell[D];
+                        float t[D], w[kSide];
+                        locate<D>(x, P.res[lg + j], cell, t);
+                        side_weights<D>(t, side, w);
 #pragma unroll
                         for (int f2 = 0; f2 < F / 2; ++f2) {
                             float lo_sum = 0.f, hi_sum = 0.f;
@@ -235,11 +262,11 @@ field_fwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, cons
                             for (int c = 0; c < kSide; ++c) {
                                 const float2 pair = unpack_pair<T>(e[j][c][f2]);
                                 if (c == 0) {
-                                    lo_sum = __fmul_rn(w[j][0], pair.x);
-                                    hi_sum = __fmul_rn(w[j][0], pair.y);
+                                    lo_sum = __fmul_rn(w[0], pair.x);
+                                    hi_sum = __fmul_rn(w[0], pair.y);
                                 } else {
-                                    lo_sum = __fadd_rn(lo_sum, __fmul_rn(w[j][c], pair.x));
-                                    hi_sum = __fadd_rn(hi_sum, __fmul_rn(w[j][c], pair.y));
+                                    lo_sum = __fadd_rn(lo_sum, __fmul_rn(w[c], pair.x));
+                                    hi_sum = __fadd_rn(hi_sum, __fmul_rn(w[c], pair.y));
                                 }
                             }
                             // low-x side + high-x side
@@ -253,6 +280,14 @@ field_fwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, cons
                     const int chunk = lg / LG;
                     asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(my_row + ((chunk << 4) ^ swz) + side * 8), "r"(lo), "r"(hi) : "memory");
                     if (feat_row) __stcs(reinterpret_cast<uint2 *>(feat_row + chunk * kChunkFeats + h), make_uint2(lo, hi));
+                };
+                uint32_t ea[LG][kSide][F / 2], eb[LG][kSide][F / 2];
+                issue(0, ea);
+                for (int lg = 0; lg < n_levels; lg += 2 * LG) {  // levels * features is a multiple of 16: an even number of chunks
+                    issue(lg + LG, eb);
+                    consume(lg, ea);
+                    if (lg + 2 * LG < n_levels) issue(lg + 2 * LG, ea);
+                    consume(lg + LG, eb);
                 }
             }
             fence_async_smem();  // the tensor core reads the tile through the async proxy
@@ -260,7 +295,6 @@ field_fwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, cons
         }
     } else {
         // ================= row group: the MLP on a tile, in place in its ring buffer =================
-        regs_for_row_group();
         const int t = threadIdx.x - kUnits * kUnitThreads;
         const int g = t / kRowThreads, row = t % kRowThreads, warp = row >> 5;
         const bool issuer = warp == 0;
@@ -270,7 +304,7 @@ field_fwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, cons
         const float *bias = reinterpret_cast<const float *>(smem + PL.bias_offset);
         uint32_t phase = 0;
         float loss = 0.f;
-        for (long long q = g; q < n_mine; q += kRowGroups) {
+        for (long long q = g; q < n_mine; q += kFwdRowGroups) {
             const int r = static_cast<int>(q % kRing);
             unsigned char *tile = smem + r * kTileBytes;
             const uint32_t tile_addr = smem_addr(tile);
@@ -293,7 +327,7 @@ field_fwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, cons
                 const bool ok = rows_wait_mma(bar, phase, abort_now, bar_rows(g), issued);
                 const float *layer_bias = bias + l * kMaxDim;
                 if (ok && l < s.depth) {
-                    drain_row<T, ACT, BIAS>(taddr, out_pad, layer_bias, [&](int chunk, uint4 packed) {
+                    drain_row16<T, ACT, BIAS>(taddr, out_pad, layer_bias, [&](int chunk, uint4 packed) {
                         st_shared_16(row_addr + ((chunk << 4) ^ row_swizzle), packed);
                     });
                     fence_async_smem();
@@ -305,7 +339,7 @@ field_fwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, cons
                         const T *target_row = static_cast<const T *>(mse.target) + rr * mse.target_stride;
                         T *grad_row = static_cast<T *>(mse.grad) + rr * mse.grad_stride;
                         T *out_row = y ? y + rr * y_stride : nullptr;
-                        drain_row<T, TH_ACT_NONE, BIAS>(taddr, out_pad, layer_bias, [&](int chunk, uint4 packed) {
+                        drain_row16<T, TH_ACT_NONE, BIAS>(taddr, out_pad, layer_bias, [&](int chunk, uint4 packed) {
                             if (live && 8 * chunk < s.d_out) {
                                 if (out_row) __stcs(reinterpret_cast<uint4 *>(out_row + 8 * chunk), packed);
                                 const uint4 tg = __ldcs(reinterpret_cast<const uint4 *>(target_row + 8 * chunk));
@@ -314,7 +348,7 @@ field_fwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, cons
                         });
                     } else {
                         T *out_row = y + rr * y_stride;
-                        drain_row<T, TH_ACT_NONE, BIAS>(taddr, out_pad, layer_bias, [&](int chunk, uint4 packed) {
+                        drain_row16<T, TH_ACT_NONE, BIAS>(taddr, out_pad, layer_bias, [&](int chunk, uint4 packed) {
                             if (live) store_chunk_to_global<T>(out_row, chunk, s.d_out, packed, y_vec);
                         });
                     }
@@ -442,7 +476,7 @@ field_bwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, cons
 
     if (row_thread) {
         // ================= row group: features + output gradient -> weight gradients (TMEM), feature gradient (ring) =================
-        regs_for_row_group();
+        regs_take<88>();
         unsigned char *tiles = smem + g * FP.group_tiles * kTileBytes;
         auto act_tile = [&](int l) { return tiles + l * kTileBytes; };
         unsigned char *go_tile = tiles + (d + 1) * kTileBytes;
@@ -571,7 +605,7 @@ field_bwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, cons
         }
     } else {
         // ================= point unit: feature gradient of a tile -> reductions into the table gradient =================
-        regs_for_point_unit();
+        regs_give_back<56>();
         const int unit = threadIdx.x / kUnitThreads, v = threadIdx.x % kUnitThreads;
         const int lp = v >> 1, side = v & 1;
         const unsigned lane = threadIdx.x & 31u;
@@ -754,7 +788,7 @@ int launch_field_fwd(const FieldArgs &a, const void *table, void *feats, int64_t
     // a CTA keeps three point units and two row groups busy: give each a few tiles before spreading over more SMs
     const long long want = (tiles + kRing - 1) / kRing;
     const long long cap = sm_count();
-    kernel<<<static_cast<unsigned>(want < cap ? (want < 1 ? 1 : want) : cap), kFieldThreads, need, stream>>>(
+    kernel<<<static_cast<unsigned>(want < cap ? (want < 1 ? 1 : want) : cap), kFwdThreads, need, stream>>>(
         a.P, a.cv, static_cast<const T *>(table), a.n_levels, a.s, a.p, maps, use_tma, static_cast<T *>(feats), feats_stride,
         static_cast<T *>(y), y_stride, y ? rows_vector_ok(y, y_stride, a.s.d_out) : 0, mse, n);
     return launch_status("field_fwd_kernel launch");
