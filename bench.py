@@ -178,7 +178,7 @@ class TrainStep:
             enc.embeddings.uniform_(-1e-4, 1e-4)
         mlp = FullyFusedMLP(32, 64, 16, depth=2, bias=False)
         self.trainer = NeuralFieldTrainer(enc.to(device).half(), mlp.to(device).half(), lr=1e-2, betas=(0.9, 0.99), eps=1e-15,
-                                          backward_passes=args.backward_passes, fused=False if args.unfused else None)
+                                          backward_passes=args.backward_passes, fused={"auto": None, "both": True, "backward": "backward", "none": False}[args.fused])
         gen = torch.Generator(device=device).manual_seed(1234 + rank)  # a different batch per rank
         self.coords = torch.rand(points, 3, device=device, generator=gen)
         self.targets = torch.rand(points, 16, device=device, generator=gen).half()
@@ -551,7 +551,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="train_step", choices=["train_step", "hash", "mlp", "reversible", "contention"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--unfused", action="store_true", help="train_step: separate encoding and MLP kernels instead of the fused pair")
+    ap.add_argument("--fused", default="auto", choices=["auto", "both", "backward", "none"],
+                    help="train_step: which passes run in the kernels that fuse encoding and MLP (auto: the trainer's default)")
     ap.add_argument("--backward-passes", type=int, default=None,
                     help="train_step: run the encoding backward in this many level ranges with the gradient sums overlapped")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],

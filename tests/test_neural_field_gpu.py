@@ -205,8 +205,9 @@ def test_trainer_fused_and_separate_paths_see_the_same_gradients(dtype):
         loss = float(trainer.step(coords, targets))
         return loss, trainer._state.table_m.clone(), trainer._state.mlp_m.clone()
 
-    loss_a, table_a, mlp_a = moments(True)
     loss_b, table_b, mlp_b = moments(False)
-    assert abs(loss_a - loss_b) <= 1e-4 * abs(loss_b)
-    # table gradients are summed with 16-bit reductions in varying order: 11 significant bits in float16, 8 in bfloat16
-    assert nerr(table_a, table_b) <= (2e-2 if dtype == torch.float16 else 8e-2) and nerr(mlp_a, mlp_b) <= 5e-3
+    for mode in (True, "backward", None):
+        loss_a, table_a, mlp_a = moments(mode)
+        assert abs(loss_a - loss_b) <= 1e-4 * abs(loss_b)
+        # table gradients are summed with 16-bit reductions in varying order: 11 significant bits in float16, 8 in bfloat16
+        assert nerr(table_a, table_b) <= (2e-2 if dtype == torch.float16 else 8e-2) and nerr(mlp_a, mlp_b) <= 5e-3

@@ -15,15 +15,18 @@
 //                      with vector reductions (the arithmetic of hash_bwd_kernel), the leading dense levels
 //                      accumulated per CTA in shared memory and flushed once.
 //
-// Why one kernel: the encoding is bound by the SM-to-L2 request path (one request per clock per SM)
-// with the tensor pipe idle, the MLP by a chain of short tensor-core steps with that path idle.  A CTA
-// (forward) or thread group (backward) alternates between the two kinds of phase on its own tile while
-// the others on the SM are in the other kind, so the MLP's time hides under the encoding's.
+// Why one kernel: the encoding is bound by the SM-to-L2 request path (one request per clock per SM) with the
+// tensor pipe idle, the MLP by a chain of short tensor-core steps with that path idle; in one kernel the
+// MLP's time can hide under the encoding's, and the feature matrix and its gradient stay on chip.  What it
+// costs: the stand-alone encoding kernels need all of an SM's registers (32 warps of 64) to keep that path
+// busy, and every warp given to the MLP is one they lose.
 //
-// Forward: 256-thread CTAs, up to four per SM, each with one operand tile, its own copy of the
-// weights and 64 TMEM columns.  Backward: one CTA per SM made of independent GROUPS of threads that
-// synchronise with named barriers; a group owns its operand tiles and 256 TMEM columns, the groups
-// share the weights and the shared-memory copy of the coarse levels.
+// Forward: one CTA per SM, three point units (gathers) and one row group (MLP) that hand tiles over through a
+// ring of operand tiles; two bursts of gathers in flight per lane make up for the smaller number of warps.
+// Backward: one CTA per SM made of two independent GROUPS of 512 threads that synchronise with named
+// barriers; a group alternates between its MLP phase (256 of its threads) and its scatter phase (all 512),
+// owns its operand tiles and 256 TMEM columns, and shares the weights and the shared-memory copy of the
+// coarse levels with the other group.
 //
 // Every mbarrier wait is bounded; a wait that runs out raises the status word th_mlp_tc_status reads,
 // the CTA stops working, keeps its barrier sequence, frees its TMEM and returns.
@@ -36,39 +39,26 @@ namespace {
 constexpr int kTilePoints = kTileRows;  // 128 points = 128 MLP rows
 constexpr int kChunkFeats = 8;          // features in one 16-byte chunk of a 16-bit row
 
-// ---- thread roles ---------------------------------------------------------------------------------
+// ---- forward: thread roles ---------------------------------------------------------------------------
 //
-// Both kernels run ONE CTA of 1024 threads per SM, split into
-//   3 point units of 256 threads   two lanes per point, 128 points: the encoding's gathers (forward) or
-//                                  reductions (backward)
-//   2 row groups of 128 threads    thread = tile row = TMEM lane, warp 0 of the group issues the MMAs: the MLP
-// A tile goes from one side to the other through a ring of 6 buffers in shared memory.  The CTA's tiles are
-// numbered 0, 1, 2, ...; tile q uses buffer q % 6, is handled by point unit q % 3 and by row group q % 2, so a
-// buffer always has the same two parties and two named barriers: FULL[r] (producer arrives, consumer waits)
-// and EMPTY[r] (consumer arrives, producer waits, from the second use on).  Nobody else ever waits for
-// anybody: while a row group walks a tile through its layers, the point units keep the SM-to-L2 request
-// path busy, which is what bounds the encoding.
+// ONE CTA of 896 threads per SM:
+//   3 point units of 256 threads   two lanes per point, 128 points: the encoding's gathers
+//   1 row group of 128 threads     thread = tile row = TMEM lane, warp 0 issues the MMAs: the MLP
+// A tile goes from a point unit to the row group through a ring of 6 operand tiles in shared memory.  The
+// CTA's tiles are numbered 0, 1, 2, ...; tile q uses buffer q % 6 and is written by point unit q % 3, so a
+// buffer always has the same two parties and two named barriers: FULL[r] (the unit arrives, the row group
+// waits) and EMPTY[r] (the row group arrives, the unit waits, from the buffer's second use on).  Nobody else
+// ever waits for anybody: while the row group walks a tile through its layers, the point units keep the
+// SM-to-L2 request path busy, which is what bounds the encoding.
 constexpr int kUnits = 3, kUnitThreads = 256;
-constexpr int kRowGroups = 2, kRowThreads = 128;
+constexpr int kRowGroups = 1, kRowThreads = 128;
 constexpr int kRing = 6;
-constexpr int kFieldThreads = kUnits * kUnitThreads + kRowGroups * kRowThreads;
-static_assert(kFieldThreads == 1024 && kRing % kUnits == 0 && kRing % kRowGroups == 0, "role split");
+static_assert(kRing % kUnits == 0 && kRing % kRowGroups == 0, "a ring buffer keeps its producer and its consumer");
 constexpr int kHandOver = kUnitThreads + kRowThreads;  // threads meeting at a FULL / EMPTY barrier
 
 __device__ __forceinline__ int bar_full(int r) { return 1 + r; }
 __device__ __forceinline__ int bar_empty(int r) { return 1 + kRing + r; }
 __device__ __forceinline__ int bar_rows(int g) { return 1 + 2 * kRing + g; }
-
-// Register budget per role (setmaxnreg moves registers between warpgroups of a running CTA).
-//   backward: 1024 threads launched with 64 registers each; the point units (6 warpgroups) give 8 each back and
-//             the two row groups, whose epilogues hold 32 accumulator columns at a time, take 24 more:
-//             768 x 56 + 256 x 88 = 65 536.
-//   forward:  the gathers keep two bursts of 16 rows in flight per lane and want 72 registers, so the forward runs
-//             ONE row group: 896 threads with 72 registers each, no rebalancing.
-template <int REGS>
-__device__ __forceinline__ void regs_give_back() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS) : "memory"); }
-template <int REGS>
-__device__ __forceinline__ void regs_take() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS) : "memory"); }
 
 __device__ __forceinline__ void named_barrier(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
@@ -144,8 +134,7 @@ __device__ __forceinline__ void field_teardown(uint32_t tmem, uint32_t tmem_cols
 // pass).  Row groups consume: the layers run in place in the ring buffer, the last epilogue writes the
 // prediction or (prediction - target) * scale and sums the squared error.
 
-constexpr int kFwdRowGroups = 1;
-constexpr int kFwdThreads = kUnits * kUnitThreads + kFwdRowGroups * kRowThreads;
+constexpr int kFwdThreads = kUnits * kUnitThreads + kRowGroups * kRowThreads;
 
 template <typename T, int D, int F, int ACT, bool BIAS>
 __global__ void __launch_bounds__(kFwdThreads, 1)
@@ -163,7 +152,7 @@ field_fwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, cons
     __shared__ int abort_flag;
     const TcPlan PL = tc_plan(s, false, kRing);  // kRing operand tiles, then weights and biases
     constexpr int bf16 = std::is_same<T, __half>::value ? 0 : 1;
-    constexpr uint32_t kTmemCols = 64 * kFwdRowGroups;  // 64 accumulator columns per row group (a power of two >= 32)
+    constexpr uint32_t kTmemCols = 64 * kRowGroups;  // 64 accumulator columns per row group (a power of two >= 32)
     volatile int *abort_now = &abort_flag;
 
     if (threadIdx.x == 0) abort_flag = 0;
@@ -304,7 +293,7 @@ field_fwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, cons
         const float *bias = reinterpret_cast<const float *>(smem + PL.bias_offset);
         uint32_t phase = 0;
         float loss = 0.f;
-        for (long long q = g; q < n_mine; q += kFwdRowGroups) {
+        for (long long q = g; q < n_mine; q += kRowGroups) {
             const int r = static_cast<int>(q % kRing);
             unsigned char *tile = smem + r * kTileBytes;
             const uint32_t tile_addr = smem_addr(tile);
@@ -366,92 +355,103 @@ field_fwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, cons
     field_teardown(tmem_base, kTmemCols);
 }
 
+// Thread groups that share an SM start in step and would stay in step - all of them scattering, then all of
+// them in their MLP phase with the request path idle.  Each therefore waits a different fraction of a tile
+// period once, at the start, so that their MLP phases interleave from then on.
+__device__ __forceinline__ void stagger_start(long long cycles) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < cycles) __nanosleep(200);
+}
+
 // ---- backward -------------------------------------------------------------------------------------
 //
-// Row groups are the producers here.  A group owns d + 2 operand tiles (depth d): act[0] = features,
-// act[l] = input of layer l (recomputed), and one tile for the output gradient.  Going down the layers, dz of
-// layer l - 1 is written IN PLACE over act[l] once the MMAs that read act[l] have finished (dgrad and wgrad
-// of a step are committed and awaited together); weight gradients stay in the group's TMEM columns for the
-// whole kernel.  The feature gradient of a tile leaves the accumulator as 16-bit rows into a ring buffer
-// (rows `pitch` bytes apart, 16-byte chunks XOR-swizzled so that neither side has bank conflicts), where a
-// point unit picks it up and issues the reductions: weight * gradient into the table gradient, level 0
-// (every point hits its few thousand rows) into a CTA-private copy in shared memory that is flushed once.
+// One CTA per SM, G groups of NT threads.  Threads 0..255 of a group are its MLP threads (thread = tile
+// row x column half, warp 0 issues the MMAs); all NT threads scatter.  A group's barriers: id 1 + 2g for
+// all NT threads, id 2 + 2g for the 256 MLP threads.
+//
+// Operand tiles of a group (depth d): act[0] = features, act[l] = input of layer l (recomputed), and one
+// tile for the output gradient.  Going down the layers, dz of layer l - 1 is written IN PLACE over
+// act[l] once the MMAs that read act[l] have finished (dgrad and wgrad of a step are committed and
+// awaited together), and the feature gradient of the tile ends up, in the operand layout, in act[1]'s
+// buffer, where the scatter phase reads it: d + 2 tiles per group.
 
 struct FieldBwdPlan {
-    int group_tiles;    // operand tiles per row group
-    int ring;           // byte offset of the feature-gradient ring (after the groups' tiles)
-    int ring_pitch;     // bytes per row in a ring buffer: 64 (up to 32 features) or 128
-    int ring_each;
-    int weights;        // byte offset of the weight tiles
+    int group_tiles;    // operand tiles per group
+    int weights;        // byte offset of the weight tiles (after all groups' tiles)
     int coarse;         // byte offset of the shared-memory copy of the coarse levels
     int coarse_bytes;
     int total;
-    TcPlan w;           // weight offsets relative to `weights`: a forward-style plan with zero activation tiles
+    TcPlan w;           // weight offsets relative to `weights` come from a forward-style plan with zero tiles
 };
 
 __host__ __device__ inline FieldBwdPlan field_bwd_plan(const MlpShape &s, int groups, int coarse_bytes) {
     FieldBwdPlan f{};
     f.group_tiles = s.depth + 2;
-    f.ring = groups * f.group_tiles * kTileBytes;
-    f.ring_pitch = s.ki <= 32 ? 64 : 128;
-    f.ring_each = kTileRows * f.ring_pitch;
-    f.weights = f.ring + kRing * f.ring_each;
-    f.w = tc_plan(s, false, 0);
+    f.weights = groups * f.group_tiles * kTileBytes;
+    f.w = tc_plan(s, false, 0);  // act_tiles = 0: offsets count from the first weight tile
     f.coarse = f.weights + ((f.w.total + 15) & ~15);
     f.coarse_bytes = (coarse_bytes + 15) & ~15;
     f.total = f.coarse + f.coarse_bytes;
     return f;
 }
 
-// byte offset of 16-byte chunk c of row r in a ring buffer
-__device__ __forceinline__ uint32_t ring_offset(int pitch, int r, int c) {
-    return pitch == 64 ? r * 64 + ((c ^ ((r >> 1) & 3)) << 4) : r * 128 + ((c ^ (r & 7)) << 4);
-}
 
-// One layer's weight-gradient accumulator of a 128-thread row group (M = 64 layout: gradient row m sits in
-// TMEM lane 32 * (m / 16) + m % 16, so lanes 0..15 of warp w carry rows 16 w .. 16 w + 15) -> float32 sums.
-__device__ __forceinline__ void flush_dw_rows(uint32_t taddr, int warp, int lane, int pad, float *dst, int out_dim, int in_dim) {
-    const int m = 16 * warp + lane;
-    for (int first = 0; first < pad; first += 16) {
-        uint32_t raw[32];
-        tmem_ld16(taddr + first, raw);
-        tmem_ld_wait();
-        if (lane < 16 && m < out_dim) {
-#pragma unroll
-            for (int k = 0; k < 16; ++k)
-                if (first + k < in_dim) atomicAdd(dst + m * in_dim + first + k, __uint_as_float(raw[k]));
+// The group's MLP threads wait for the MMAs committed to `mbar`: the warp that issued them polls
+// (bounded; `poller` is false when nothing was issued), the others park at the MLP barrier.  False for
+// every thread alike when a wait ran out somewhere in the CTA.
+__device__ __forceinline__ bool group_wait_mma(uint32_t mbar, uint32_t &phase, volatile int *abort_flag, int barrier_id, bool poller) {
+    if (poller) {
+        if (!mbar_wait(mbar, phase)) {
+            *abort_flag = 1;
+            g_tc_status = 1;
         }
+        tc_fence_after();
+        tc_fence_before();
     }
+    phase ^= 1;
+    named_barrier(barrier_id, kTcThreads);
+    tc_fence_after();
+    return *abort_flag == 0;
 }
 
-template <typename T, int D, int F, int ACT>
-__global__ void __launch_bounds__(kFieldThreads, 1)
+template <typename T, int D, int F, int ACT, int G, int NT>
+__global__ void __launch_bounds__(G * NT, 1)
 field_bwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, const int n_levels, const int coarse_end,
                  const MlpShape s, const MlpParams p, const __grid_constant__ WeightMaps maps, const int use_tma,
                  const T *__restrict__ feats, const long long feats_stride, const T *__restrict__ go, const long long go_stride,
                  T *__restrict__ grad_table, T *__restrict__ gx, const long long gx_stride, float *__restrict__ workspace,
-                 const long long n_points, const int vec_bits, const int n_groups) {
-    // n_groups: row groups at work (2, or 1 when a deep network's accumulators and tiles leave room for one only)
+                 const long long n_points, const int vec_bits, const int stagger_cycles) {
     constexpr int LG = kChunkFeats / F;
     constexpr int kSide = 1 << (D - 1);
+    constexpr int kHalves = NT / kTcThreads;  // how many ways a group splits a tile's chunks in the scatter phase
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint32_t tmem_holder;
-    __shared__ __align__(8) unsigned long long mbars[kRowGroups];
+    __shared__ __align__(8) unsigned long long mbars[G];
     __shared__ __align__(8) unsigned long long wbar;
     __shared__ int abort_flag;
     const int d = s.depth;
     unsigned long long coarse_rows = 0;
     if (coarse_end > 0) coarse_rows = P.offset[coarse_end - 1] + P.rows[coarse_end - 1] - P.offset[0];
-    const FieldBwdPlan FP = field_bwd_plan(s, n_groups, static_cast<int>(coarse_rows * F * sizeof(T)));
+    const FieldBwdPlan FP = field_bwd_plan(s, G, static_cast<int>(coarse_rows * F * sizeof(T)));
     constexpr int bf16 = std::is_same<T, __half>::value ? 0 : 1;
-    const int group_cols = tc_plan(s, true).tmem_cols;  // dgrad accumulator + one weight-gradient accumulator per layer
+    const TcPlan BP = tc_plan(s, true);  // TMEM columns of a group: dgrad accumulator + one weight-gradient accumulator per layer
+    const int group_cols = BP.tmem_cols;
+
+    const int group = threadIdx.x / NT, u = threadIdx.x % NT;
+    const bool mlp_thread = u < kTcThreads;
+    const int bar_all = 1 + 2 * group, bar_mlp = 2 + 2 * group;
     volatile int *abort_now = &abort_flag;
 
-    if (threadIdx.x == 0) abort_flag = 0;
-    // operand tiles, ring and the coarse copy start as zeros
-    for (int e = threadIdx.x; e < FP.weights / 16; e += kFieldThreads) reinterpret_cast<uint4 *>(smem)[e] = make_uint4(0, 0, 0, 0);
-    for (int e = threadIdx.x; e < FP.coarse_bytes / 16; e += kFieldThreads) reinterpret_cast<uint4 *>(smem + FP.coarse)[e] = make_uint4(0, 0, 0, 0);
+    // ---- set-up ----
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int g = 0; g < G; ++g)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&mbars[g])), "r"(1u) : "memory");
+    }
+    // operand tiles and the coarse copy start as zeros
+    for (int e = threadIdx.x; e < FP.weights / 16; e += G * NT) reinterpret_cast<uint4 *>(smem)[e] = make_uint4(0, 0, 0, 0);
+    for (int e = threadIdx.x; e < FP.coarse_bytes / 16; e += G * NT) reinterpret_cast<uint4 *>(smem + FP.coarse)[e] = make_uint4(0, 0, 0, 0);
     unsigned char *wsmem = smem + FP.weights;
     bool weights_ok = true;
     if (use_tma) {
@@ -460,75 +460,94 @@ field_bwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, cons
         if (threadIdx.x < kTcThreads) stage_all_weights<T>(wsmem, FP.w, s, p);  // its loops stride by kTcThreads
         __syncthreads();
     }
-    const uint32_t tmem_base = field_setup(&tmem_holder, mbars, &abort_flag, static_cast<uint32_t>(n_groups * group_cols), weights_ok);
+    if (threadIdx.x < 32) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_holder)),
+                     "r"(static_cast<uint32_t>(G * group_cols))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (!weights_ok) {
+        abort_flag = 1;
+        g_tc_status = 1;
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_holder + group * group_cols;
 
-    T *coarse_acc = reinterpret_cast<T *>(smem + FP.coarse);
-    const long long n_tiles = (n_points + kTilePoints - 1) / kTilePoints;
-    const long long first_tile = blockIdx.x, tile_stride = gridDim.x;
-    const long long n_mine = first_tile < n_tiles ? (n_tiles - first_tile + tile_stride - 1) / tile_stride : 0;
+    unsigned char *tiles = smem + group * FP.group_tiles * kTileBytes;
+    auto act_tile = [&](int l) { return tiles + l * kTileBytes; };
+    unsigned char *go_tile = tiles + (d + 1) * kTileBytes;
     auto dw_col = [&](int l) { return kAccCols + (l == 0 ? 0 : s.ki + (l - 1) * s.h); };
-    const bool row_thread = threadIdx.x >= kUnits * kUnitThreads;
-    const int t = threadIdx.x - kUnits * kUnitThreads;
-    const int g = row_thread ? t / kRowThreads : 0, row = row_thread ? t % kRowThreads : 0, warp = row >> 5;
-    const uint32_t tmem = tmem_base + g * group_cols;
-    const uint32_t taddr = tmem + (static_cast<uint32_t>(32 * warp) << 16);
-    bool accumulated = false;
+    auto weight_addr = [&](int l) { return smem_addr(weight_tile(wsmem, FP.w, s, l)); };
+    T *coarse_acc = reinterpret_cast<T *>(smem + FP.coarse);
+    const uint32_t bar = smem_addr(&mbars[group]);
+    uint32_t phase = 0;
+    const Seat seat_raw;  // built from threadIdx.x: valid for group-local use only through the fields below
+    Seat seat = seat_raw;
+    {
+        const int warp = u >> 5;
+        seat.row = 32 * (warp & 3) + (u & 31);
+        seat.group = (warp >> 2) & 1;
+        seat.lane_base = static_cast<uint32_t>(32 * (warp & 3)) << 16;
+    }
+    const uint32_t taddr = tmem + seat.lane_base;
+    const bool issuer = u < 32;
 
-    if (row_thread) {
-        // ================= row group: features + output gradient -> weight gradients (TMEM), feature gradient (ring) =================
-        regs_take<88>();
-        unsigned char *tiles = smem + g * FP.group_tiles * kTileBytes;
-        auto act_tile = [&](int l) { return tiles + l * kTileBytes; };
-        unsigned char *go_tile = tiles + (d + 1) * kTileBytes;
-        auto weight_addr = [&](int l) { return smem_addr(weight_tile(wsmem, FP.w, s, l)); };
-        const uint32_t bar = smem_addr(&mbars[g]);
-        uint32_t phase = 0;
-        const bool issuer = warp == 0;
-        // rows that can be moved as whole 16-byte chunks (checked by the launcher): bit 0 features, 1 output gradient, 2 feature gradient
-        const bool x_vec = vec_bits & 1, go_vec = vec_bits & 2, gx_vec = vec_bits & 4;
-        const int chunks_x = s.ki / 8, chunks_g = s.no / 8;
-        const uint32_t row_off = row * 128, row_swizzle = (row & 7) << 4;
-        for (long long q = g; q < n_mine && g < n_groups; q += n_groups) {
-            const int r = static_cast<int>(q % kRing);
-            const long long row0 = (first_tile + q * tile_stride) * kTileRows;
-            if (!*abort_now) {
+    const long long n_tiles = (n_points + kTilePoints - 1) / kTilePoints;
+    bool accumulated = false;
+    // rows that can be moved as whole 16-byte chunks (checked by the launcher): bit 0 features, 1 output gradient, 2 feature gradient
+    const bool x_vec = vec_bits & 1, go_vec = vec_bits & 2, gx_vec = vec_bits & 4;
+
+    if (G > 1 && group > 0) stagger_start(static_cast<long long>(group) * stagger_cycles);
+
+    for (long long tile = static_cast<long long>(blockIdx.x) * G + group; tile < n_tiles; tile += static_cast<long long>(gridDim.x) * G) {
+        const long long row0 = tile * kTileRows;
+        const bool dead = *abort_now != 0;  // keep the barrier sequence, do no work
+        // ================= MLP phase (the group's first 256 threads) =================
+        if (mlp_thread) {
+            if (!dead) {
                 if (x_vec && go_vec) {
-                    for (int id = row; id < kTileRows * chunks_x; id += kRowThreads) {
-                        const int rr = id / chunks_x, c = id - rr * chunks_x;
-                        const long long grow = row0 + rr;
-                        const bool inside = grow < n_points && 8 * c < s.d_in;
-                        const T *src = inside ? feats + grow * feats_stride + 8 * c : feats;
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(chunk_ptr(act_tile(0), rr, c))), "l"(src), "r"(inside ? 16 : 0) : "memory");
+                    // cp.async by the 256 MLP threads (tc_tiles.cuh strides by kTcThreads and uses threadIdx.x: pass u through a shifted copy)
+                    const int chunks_x = s.ki / 8, chunks_g = s.no / 8;
+                    for (int id = u; id < kTileRows * chunks_x; id += kTcThreads) {
+                        const int r = id / chunks_x, c = id - r * chunks_x;
+                        const long long row = row0 + r;
+                        const bool inside = row < n_points && 8 * c < s.d_in;
+                        const T *src = inside ? feats + row * feats_stride + 8 * c : feats;
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(chunk_ptr(act_tile(0), r, c))), "l"(src), "r"(inside ? 16 : 0) : "memory");
                     }
-                    for (int id = row; id < kTileRows * chunks_g; id += kRowThreads) {
-                        const int rr = id / chunks_g, c = id - rr * chunks_g;
-                        const long long grow = row0 + rr;
-                        const bool inside = grow < n_points && 8 * c < s.d_out;
-                        const T *src = inside ? go + grow * go_stride + 8 * c : go;
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(chunk_ptr(go_tile, rr, c))), "l"(src), "r"(inside ? 16 : 0) : "memory");
+                    for (int id = u; id < kTileRows * chunks_g; id += kTcThreads) {
+                        const int r = id / chunks_g, c = id - r * chunks_g;
+                        const long long row = row0 + r;
+                        const bool inside = row < n_points && 8 * c < s.d_out;
+                        const T *src = inside ? go + row * go_stride + 8 * c : go;
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(chunk_ptr(go_tile, r, c))), "l"(src), "r"(inside ? 16 : 0) : "memory");
                     }
                     asm volatile("cp.async.commit_group;" ::: "memory");
                     async_tile_wait();
                 } else {
-                    for (int id = row; id < kTileRows * chunks_x; id += kRowThreads) {
-                        const int rr = id / chunks_x, c = id - rr * chunks_x;
-                        const long long grow = row0 + rr;
+                    const int chunks_x = s.ki / 8, chunks_g = s.no / 8;
+                    for (int id = u; id < kTileRows * chunks_x; id += kTcThreads) {
+                        const int r = id / chunks_x, c = id - r * chunks_x;
+                        const long long row = row0 + r;
                         uint4 v = make_uint4(0, 0, 0, 0);
-                        if (grow < n_points && 8 * c < s.d_in) v = gather8(reinterpret_cast<const unsigned short *>(feats + grow * feats_stride + 8 * c), 8 * c, s.d_in);
-                        *reinterpret_cast<uint4 *>(chunk_ptr(act_tile(0), rr, c)) = v;
+                        if (row < n_points && 8 * c < s.d_in) v = gather8(reinterpret_cast<const unsigned short *>(feats + row * feats_stride + 8 * c), 8 * c, s.d_in);
+                        *reinterpret_cast<uint4 *>(chunk_ptr(act_tile(0), r, c)) = v;
                     }
-                    for (int id = row; id < kTileRows * chunks_g; id += kRowThreads) {
-                        const int rr = id / chunks_g, c = id - rr * chunks_g;
-                        const long long grow = row0 + rr;
+                    for (int id = u; id < kTileRows * chunks_g; id += kTcThreads) {
+                        const int r = id / chunks_g, c = id - r * chunks_g;
+                        const long long row = row0 + r;
                         uint4 v = make_uint4(0, 0, 0, 0);
-                        if (grow < n_points && 8 * c < s.d_out) v = gather8(reinterpret_cast<const unsigned short *>(go + grow * go_stride + 8 * c), 8 * c, s.d_out);
-                        *reinterpret_cast<uint4 *>(chunk_ptr(go_tile, rr, c)) = v;
+                        if (row < n_points && 8 * c < s.d_out) v = gather8(reinterpret_cast<const unsigned short *>(go + row * go_stride + 8 * c), 8 * c, s.d_out);
+                        *reinterpret_cast<uint4 *>(chunk_ptr(go_tile, r, c)) = v;
                     }
                 }
             }
             fence_async_smem();
             tc_fence_before();
-            named_barrier(bar_rows(g), kRowThreads);
+            named_barrier(bar_mlp, kTcThreads);
             // ---- recompute the forward, keeping every layer's input ----
             for (int l = 0; l < d; ++l) {
                 bool issued = false;
@@ -541,13 +560,11 @@ field_bwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, cons
                     __syncwarp();
                     issued = true;
                 }
-                if (rows_wait_mma(bar, phase, abort_now, bar_rows(g), issued)) {
-                    const uint32_t dst = smem_addr(act_tile(l + 1)) + row_off;
-                    drain_row<T, ACT, false>(taddr, s.h, nullptr, [&](int chunk, uint4 packed) { st_shared_16(dst + ((chunk << 4) ^ row_swizzle), packed); });
-                }
+                if (group_wait_mma(bar, phase, abort_now, bar_mlp, issued))
+                    hidden_epilogue<T, ACT, false>(taddr, seat, s.h, nullptr, act_tile(l + 1));
                 fence_async_smem();
                 tc_fence_before();
-                named_barrier(bar_rows(g), kRowThreads);
+                named_barrier(bar_mlp, kTcThreads);
             }
             // ---- down the layers: dgrad + wgrad per step ----
             for (int l = d; l >= 0; --l) {
@@ -565,54 +582,30 @@ field_bwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, cons
                     __syncwarp();
                     issued = true;
                 }
-                const bool ok = rows_wait_mma(bar, phase, abort_now, bar_rows(g), issued);
-                if (l > 0) {
-                    if (ok) {
-                        // dz of the layer below = dy * act'(its parked output), in place over that output
-                        const uint32_t parked = smem_addr(act_tile(l)) + row_off;
-                        drain_row<T, TH_ACT_NONE, false>(taddr, in_pad, nullptr, [&](int chunk, uint4 gq) {
-                            const uint32_t off = (chunk << 4) ^ row_swizzle;
-                            if constexpr (ACT == TH_ACT_RELU) {
-                                const uint4 a = ld_shared_16(parked + off);
-                                gq.x = keep_where_positive<T>(gq.x, a.x);
-                                gq.y = keep_where_positive<T>(gq.y, a.y);
-                                gq.z = keep_where_positive<T>(gq.z, a.z);
-                                gq.w = keep_where_positive<T>(gq.w, a.w);
-                            }
-                            st_shared_16(parked + off, gq);
-                        });
+                if (group_wait_mma(bar, phase, abort_now, bar_mlp, issued)) {
+                    if (l > 0) {
+                        dz_epilogue<T, ACT>(taddr, seat, in_pad, act_tile(l), act_tile(l));  // in place: mask from the parked activation
+                    } else {
+                        // the tile's feature gradient, rounded to T, in the operand layout in act[1]'s buffer
+                        hidden_epilogue<T, TH_ACT_NONE, false>(taddr, seat, in_pad, nullptr, act_tile(1));
+                        if (gx) {
+                            const bool live = row0 + seat.row < n_points;
+                            dx_epilogue<T>(taddr, seat, in_pad, gx + (live ? row0 + seat.row : 0) * gx_stride, s.d_in, live, gx_vec);
+                        }
                     }
-                } else {
-                    // the tile's feature gradient, rounded to T, into ring buffer r once its previous tile has been read
-                    if (q >= kRing) named_barrier(bar_empty(r), kHandOver);
-                    if (ok) {
-                        const uint32_t ring = smem_addr(smem + FP.ring + r * FP.ring_each);
-                        const bool live = row0 + row < n_points;
-                        T *gx_row = gx ? gx + (live ? row0 + row : 0) * gx_stride : nullptr;
-                        drain_row<T, TH_ACT_NONE, false>(taddr, in_pad, nullptr, [&](int chunk, uint4 packed) {
-                            if (8 * chunk < in_pad) st_shared_16(ring + ring_offset(FP.ring_pitch, row, chunk), packed);
-                            if (gx_row && live) store_chunk_to_global<T>(gx_row, chunk, s.d_in, packed, gx_vec);
-                        });
-                    }
-                    __threadfence_block();
-                    named_barrier_arrive(bar_full(r), kHandOver);
                 }
                 fence_async_smem();
                 tc_fence_before();
-                named_barrier(bar_rows(g), kRowThreads);
+                named_barrier(bar_mlp, kTcThreads);
             }
             accumulated = accumulated || !*abort_now;
         }
-    } else {
-        // ================= point unit: feature gradient of a tile -> reductions into the table gradient =================
-        regs_give_back<56>();
-        const int unit = threadIdx.x / kUnitThreads, v = threadIdx.x % kUnitThreads;
-        const int lp = v >> 1, side = v & 1;
-        const unsigned lane = threadIdx.x & 31u;
-        const int n_chunks = n_levels / LG;
-        for (long long q = unit; q < n_mine; q += kUnits) {
-            const int r = static_cast<int>(q % kRing);
-            const long long pt = (first_tile + q * tile_stride) * kTilePoints + lp;
+        named_barrier(bar_all, NT);  // the feature gradient is in act[1]'s buffer
+
+        // ================= scatter phase (all NT threads of the group) =================
+        if (!*abort_now) {
+            const int lp = (u % kTcThreads) >> 1, side = u & 1, half = u / kTcThreads;
+            const long long pt = row0 + lp;
             const bool live = pt < n_points;
             float x[D];
 #pragma unroll
@@ -622,99 +615,98 @@ field_bwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, cons
 #pragma unroll
                 for (int dd = 0; dd < D; ++dd) x[dd] = __fdiv_rn(x[dd], P.scale);
             }
-            named_barrier(bar_full(r), kHandOver);  // the row group has written this tile's feature gradient
-            if (!*abort_now) {
-                const uint32_t ring = smem_addr(smem + FP.ring + r * FP.ring_each);
-                for (int chunk = 0; chunk < n_chunks; ++chunk) {
-                    float g8[kChunkFeats];
-                    {
-                        const uint4 raw = ld_shared_16(ring + ring_offset(FP.ring_pitch, lp, chunk));
-                        const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
+            const unsigned lane = threadIdx.x & 31u;
+            const uint32_t grad_row = smem_addr(act_tile(1)) + lp * 128, swz = (lp & 7) << 4;
+            const int n_chunks = n_levels / LG;
+            for (int chunk = half; chunk < n_chunks; chunk += kHalves) {
+                float g8[kChunkFeats];
+                {
+                    const uint4 raw = ld_shared_16(grad_row + ((chunk << 4) ^ swz));
+                    const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const float2 f2 = unpack_pair<T>(wds[k]);
-                            g8[2 * k] = live ? f2.x : 0.f;
-                            g8[2 * k + 1] = live ? f2.y : 0.f;
-                        }
+                    for (int k = 0; k < 4; ++k) {
+                        const float2 f2 = unpack_pair<T>(wds[k]);
+                        g8[2 * k] = live ? f2.x : 0.f;
+                        g8[2 * k + 1] = live ? f2.y : 0.f;
                     }
+                }
 #pragma unroll
-                    for (int j = 0; j < LG; ++j) {
-                        const int level = chunk * LG + j;
-                        uint32_t cell[D], idx[kSide];
-                        float tt[D], w[kSide];
-                        locate<D>(x, P.res[level], cell, tt);
-                        side_weights<D>(tt, side, w);
-                        side_indices<D>(cell, P, level, side, idx);
-                        if (level < coarse_end) {
-                            // leading dense levels: private copy in shared memory, flushed once at the end
-                            T *base = coarse_acc + (P.offset[level] - P.offset[0]) * F;
-                            if (live) {
-#pragma unroll
-                                for (int c = 0; c < kSide; ++c) {
-                                    float val[F];
-#pragma unroll
-                                    for (int f = 0; f < F; ++f) val[f] = __fmul_rn(w[c], g8[j * F + f]);
-                                    smem_add_row<T, F>(base + static_cast<size_t>(idx[c]) * F, val);
-                                }
-                            }
-                            continue;
-                        }
-                        T *base = grad_table + P.offset[level] * F;
-                        // lanes on the same side of the same cell share all their rows: sum in registers first (coarse grids only)
-                        bool shared_cell = false;
-                        unsigned peers = 1u << lane;
-                        if (P.res[level] <= kAggregateMaxRes) {
-                            unsigned long long key = 0;
-                            bool packable = live;
-#pragma unroll
-                            for (int dd = 0; dd < D; ++dd) {
-                                packable = packable && cell[dd] < (1u << 20);
-                                key = (key << 20) | (cell[dd] & 0xfffffu);
-                            }
-                            key = (key << 1) | static_cast<unsigned>(side);
-                            if (!packable) key = (1ull << 63) | lane;
-                            peers = __match_any_sync(0xffffffffu, key);
-                            shared_cell = __any_sync(0xffffffffu, (peers & (peers - 1)) != 0);
-                        }
-                        if (!shared_cell) {
-                            if (live) {
-#pragma unroll
-                                for (int c = 0; c < kSide; ++c) {
-                                    float val[F];
-#pragma unroll
-                                    for (int f = 0; f < F; ++f) val[f] = __fmul_rn(w[c], g8[j * F + f]);
-                                    red_add_row<F>(base + static_cast<size_t>(idx[c]) * F, val);
-                                }
-                            }
-                        } else {
-                            const bool leader = (peers & ((1u << lane) - 1u)) == 0;
-                            const int steps = __reduce_max_sync(0xffffffffu, __popc(peers));
+                for (int j = 0; j < LG; ++j) {
+                    const int level = chunk * LG + j;
+                    uint32_t cell[D], idx[kSide];
+                    float t[D], w[kSide];
+                    locate<D>(x, P.res[level], cell, t);
+                    side_weights<D>(t, side, w);
+                    side_indices<D>(cell, P, level, side, idx);
+                    if (level < coarse_end) {
+                        // leading dense levels: private copy in shared memory, flushed once at the end
+                        T *base = coarse_acc + (P.offset[level] - P.offset[0]) * F;
+                        if (live) {
 #pragma unroll
                             for (int c = 0; c < kSide; ++c) {
-                                float val[F], sum[F];
+                                float v[F];
+#pragma unroll
+                                for (int f = 0; f < F; ++f) v[f] = __fmul_rn(w[c], g8[j * F + f]);
+                                smem_add_row<T, F>(base + static_cast<size_t>(idx[c]) * F, v);
+                            }
+                        }
+                        continue;
+                    }
+                    T *base = grad_table + P.offset[level] * F;
+                    // lanes on the same side of the same cell share all their rows: sum in registers first (coarse grids only)
+                    bool shared_cell = false;
+                    unsigned peers = 1u << lane;
+                    if (P.res[level] <= kAggregateMaxRes) {
+                        unsigned long long key = 0;
+                        bool packable = live;
+#pragma unroll
+                        for (int dd = 0; dd < D; ++dd) {
+                            packable = packable && cell[dd] < (1u << 20);
+                            key = (key << 20) | (cell[dd] & 0xfffffu);
+                        }
+                        key = (key << 1) | static_cast<unsigned>(side);
+                        if (!packable) key = (1ull << 63) | lane;
+                        peers = __match_any_sync(0xffffffffu, key);
+                        shared_cell = __any_sync(0xffffffffu, (peers & (peers - 1)) != 0);
+                    }
+                    if (!shared_cell) {
+                        if (live) {
+#pragma unroll
+                            for (int c = 0; c < kSide; ++c) {
+                                float v[F];
+#pragma unroll
+                                for (int f = 0; f < F; ++f) v[f] = __fmul_rn(w[c], g8[j * F + f]);
+                                red_add_row<F>(base + static_cast<size_t>(idx[c]) * F, v);
+                            }
+                        }
+                    } else {
+                        const bool leader = (peers & ((1u << lane) - 1u)) == 0;
+                        const int steps = __reduce_max_sync(0xffffffffu, __popc(peers));
+#pragma unroll
+                        for (int c = 0; c < kSide; ++c) {
+                            float v[F], sum[F];
+#pragma unroll
+                            for (int f = 0; f < F; ++f) {
+                                v[f] = __fmul_rn(w[c], g8[j * F + f]);
+                                sum[f] = 0.f;
+                            }
+                            unsigned rest = peers;
+                            for (int st = 0; st < steps; ++st) {
+                                const int src = rest ? (__ffs(rest) - 1) : static_cast<int>(lane);
 #pragma unroll
                                 for (int f = 0; f < F; ++f) {
-                                    val[f] = __fmul_rn(w[c], g8[j * F + f]);
-                                    sum[f] = 0.f;
+                                    const float pv = __shfl_sync(0xffffffffu, v[f], src);
+                                    if (rest) sum[f] += pv;
                                 }
-                                unsigned rest = peers;
-                                for (int st = 0; st < steps; ++st) {
-                                    const int src = rest ? (__ffs(rest) - 1) : static_cast<int>(lane);
-#pragma unroll
-                                    for (int f = 0; f < F; ++f) {
-                                        const float pv = __shfl_sync(0xffffffffu, val[f], src);
-                                        if (rest) sum[f] += pv;
-                                    }
-                                    rest &= rest - 1;
-                                }
-                                if (live && leader) red_add_row<F>(base + static_cast<size_t>(idx[c]) * F, sum);
+                                rest &= rest - 1;
                             }
+                            if (live && leader) red_add_row<F>(base + static_cast<size_t>(idx[c]) * F, sum);
                         }
                     }
                 }
             }
-            if (q + kRing < n_mine) named_barrier_arrive(bar_empty(r), kHandOver);  // the buffer may take the CTA's tile q + 6
         }
+        named_barrier(bar_all, NT);  // act[1]'s buffer may be overwritten by the next tile
     }
 
     // ---- flush: weight gradients from TMEM, coarse levels from shared memory ----
@@ -722,28 +714,32 @@ field_bwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, cons
     __syncthreads();
     tc_fence_after();
     if (!abort_flag) {
-        if (row_thread && accumulated) {
+        if (mlp_thread && accumulated) {
             const MlpGradWorkspace W = grad_workspace_layout(s, workspace);
             for (int l = 0; l <= d; ++l) {
                 const int in_pad = l == 0 ? s.ki : s.h;
                 const int in_dim = l == 0 ? s.d_in : s.d_hid, out_dim = l == d ? s.d_out : s.d_hid;
                 float *dst = W.base + (l == 0 ? W.w_in : (l == d ? W.w_out : W.w_hid + (l - 1) * s.d_hid * s.d_hid));
-                flush_dw_rows(taddr + dw_col(l), warp, threadIdx.x & 31, in_pad, dst, out_dim, in_dim);
+                // flush_dw reads threadIdx.x for lane and warp: group-local values agree with it (NT is a multiple of 128)
+                flush_dw(taddr + dw_col(l), seat, in_pad, dst, out_dim, in_dim);
             }
         }
         T *dst = grad_table + P.offset[0] * F;
-        for (unsigned long long rr = threadIdx.x; rr < coarse_rows; rr += kFieldThreads) {
-            float val[F];
+        for (unsigned long long r = threadIdx.x; r < coarse_rows; r += G * NT) {
+            float v[F];
             bool any = false;
 #pragma unroll
             for (int f = 0; f < F; ++f) {
-                val[f] = to_float<T>(coarse_acc[rr * F + f]);
-                any = any || val[f] != 0.f;
+                v[f] = to_float<T>(coarse_acc[r * F + f]);
+                any = any || v[f] != 0.f;
             }
-            if (any) red_add_row<F>(dst + rr * F, val);
+            if (any) red_add_row<F>(dst + r * F, v);
         }
     }
-    field_teardown(tmem_base, static_cast<uint32_t>(n_groups * group_cols));
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x < 32)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_holder), "r"(static_cast<uint32_t>(G * group_cols)) : "memory");
 }
 
 // ---- host side ------------------------------------------------------------------------------------
@@ -794,36 +790,54 @@ int launch_field_fwd(const FieldArgs &a, const void *table, void *feats, int64_t
     return launch_status("field_fwd_kernel launch");
 }
 
-template <typename T, int D, int F, int ACT>
-int launch_field_bwd(const FieldArgs &a, const void *feats, int64_t feats_stride, const void *go, int64_t go_stride, void *grad_table,
-                     void *gx, int64_t gx_stride, float *workspace, int64_t n, cudaStream_t stream) {
+constexpr int kBwdGroupThreads = 512;
+constexpr int kFieldCoarseBudget = 72 * 1024;  // shared memory the backward sets aside for leading dense levels
+
+// A tile's reductions keep the SM's request path busy for about this many cycles: 128 points x `accesses` rows
+// each at somewhat over half a request per row (two x-neighbours mostly share one).
+int field_stagger_cycles(int accesses_per_point) { return 128 * accesses_per_point * 6 / 10; }
+
+template <typename T, int D, int F, int ACT, int kBwdGroups>
+int launch_field_bwd_groups(const FieldArgs &a, const void *feats, int64_t feats_stride, const void *go, int64_t go_stride, void *grad_table,
+                            void *gx, int64_t gx_stride, float *workspace, int64_t n, cudaStream_t stream) {
     const TcPlan BP = tc_plan(a.s, true);
-    if (BP.tmem_cols > 512) return kTcNotApplicable;
-    // two row groups when their accumulators fit the SM's tensor memory and their tiles its shared memory, else one
-    int groups = kRowGroups;
-    if (BP.tmem_cols * groups > 512 || field_bwd_plan(a.s, groups, 0).total + 2048 > kSmemBudget) groups = 1;
-    // what is left of shared memory after tiles, ring and weights goes to the coarse levels
-    const int fixed = field_bwd_plan(a.s, groups, 0).total + 2048;
-    if (fixed > kSmemBudget) return kTcNotApplicable;
-    const int coarse_end = field_coarse_end(a.P, a.n_levels, F * sizeof(T), n, kSmemBudget - fixed);
-    size_t coarse_bytes = 0;
-    for (int l = 0; l < coarse_end; ++l) coarse_bytes += static_cast<size_t>(a.P.rows[l]) * F * sizeof(T);
-    int total = field_bwd_plan(a.s, groups, static_cast<int>(coarse_bytes)).total + 1024;
+    if (BP.tmem_cols * kBwdGroups > 512) return kTcNotApplicable;
+    int budget = kFieldCoarseBudget;
+    int coarse_end = 0, total = 0;
+    for (;;) {
+        coarse_end = field_coarse_end(a.P, a.n_levels, F * sizeof(T), n, budget);
+        size_t coarse_bytes = 0;
+        for (int l = 0; l < coarse_end; ++l) coarse_bytes += static_cast<size_t>(a.P.rows[l]) * F * sizeof(T);
+        total = field_bwd_plan(a.s, kBwdGroups, static_cast<int>(coarse_bytes)).total + 1024;
+        if (total + 1024 <= kSmemBudget || coarse_end == 0) break;
+        budget /= 2;  // deep networks leave less room: give up coarse levels first
+    }
+    if (total + 1024 > kSmemBudget) return kTcNotApplicable;
     if (total < kSmemBudget / 2 + 1024) total = kSmemBudget / 2 + 1024;  // one CTA per SM: it takes all the TMEM columns it needs at once
     WeightMaps maps;
     const int use_tma = make_weight_maps(maps, a.s, a.p);
-    auto kernel = field_bwd_kernel<T, D, F, ACT>;
+    auto kernel = field_bwd_kernel<T, D, F, ACT, kBwdGroups, kBwdGroupThreads>;
     if (int rc = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, total), "cudaFuncSetAttribute(field_bwd_kernel)")) return rc;
     const long long tiles = (n + kTilePoints - 1) / kTilePoints;
-    const long long want = (tiles + kRing - 1) / kRing;
+    const long long want = (tiles + kBwdGroups - 1) / kBwdGroups;
     const long long cap = sm_count();
-    kernel<<<static_cast<unsigned>(want < cap ? (want < 1 ? 1 : want) : cap), kFieldThreads, total, stream>>>(
+    kernel<<<static_cast<unsigned>(want < cap ? want : cap), kBwdGroups * kBwdGroupThreads, total, stream>>>(
         a.P, a.cv, a.n_levels, coarse_end, a.s, a.p, maps, use_tma, static_cast<const T *>(feats), feats_stride,
         static_cast<const T *>(go), go_stride, static_cast<T *>(grad_table), static_cast<T *>(gx), gx_stride, workspace, n,
         (rows_vector_ok(feats, feats_stride, a.s.d_in) ? 1 : 0) | (rows_vector_ok(go, go_stride, a.s.d_out) ? 2 : 0) |
             (gx && rows_vector_ok(gx, gx_stride, a.s.d_in) ? 4 : 0),
-        groups);
+        field_stagger_cycles(a.n_levels * (1 << a.n_dims)));
     return launch_status("field_bwd_kernel launch");
+}
+
+// Two groups per SM when their tensor-memory columns and operand tiles fit (networks up to two hidden
+// layers of 64), one group otherwise.
+template <typename T, int D, int F, int ACT>
+int launch_field_bwd(const FieldArgs &a, const void *feats, int64_t feats_stride, const void *go, int64_t go_stride, void *grad_table,
+                     void *gx, int64_t gx_stride, float *workspace, int64_t n, cudaStream_t stream) {
+    const int rc = launch_field_bwd_groups<T, D, F, ACT, 2>(a, feats, feats_stride, go, go_stride, grad_table, gx, gx_stride, workspace, n, stream);
+    if (rc != kTcNotApplicable) return rc;
+    return launch_field_bwd_groups<T, D, F, ACT, 1>(a, feats, feats_stride, go, go_stride, grad_table, gx, gx_stride, workspace, n, stream);
 }
 
 int fill_field_args(FieldArgs &a, const void *coords, int64_t stride_n, int64_t stride_d, int coord_dtype, int n_dims, int n_feats,

@@ -26,7 +26,7 @@ With more than one process the point batch is split across ranks (every rank pas
 number of points), parameters are replicated and their gradients summed once per step.
 """
 import math
-from typing import List, Optional, Tuple
+from typing import List, Optional, Tuple, Union
 
 import torch
 import torch.distributed as dist
@@ -87,10 +87,12 @@ class NeuralFieldTrainer(nn.Module):
             overflow; Adam undoes the scale exactly.  ``None``: ``default_grad_out_scale`` of the
             global batch of the first step.
         group: process group for data parallelism (``None``: the default group, if initialised).
-        fused: direct mode only.  ``None`` (default): use the kernels that fuse the encoding with the MLP
-            when they cover the configuration, the separate operators otherwise; ``False``: always the
-            separate operators; ``True``: raise if the fused kernels do not cover the configuration.
-            ``backward_passes`` implies the separate operators.
+        fused: direct mode only; which steps run in the kernels that fuse the encoding with the MLP.
+            ``None`` (default): the backward pass when the fused kernel covers the configuration (measured
+            at benchmark configuration 3 on a B200: fused backward 1.04 ms against 0.36 + 0.78 ms for MLP
+            backward + encoding backward; fused forward 0.71 ms against 0.55 + 0.12 ms, so the forward stays
+            separate); ``"backward"``: the same, but raise if it is not covered; ``True``: forward and
+            backward fused, raise if not covered; ``False``: always the separate operators.
         backward_passes: ``None`` (default): one encoding backward, then one gradient sum over the
             ranks.  An integer n (direct mode): the encoding backward runs in n level ranges, finest
             first; the gradient rows of a finished range are summed over the ranks (NCCL,
@@ -110,10 +112,11 @@ class NeuralFieldTrainer(nn.Module):
         grad_out_scale: Optional[float] = None,
         group: Optional[dist.ProcessGroup] = None,
         backward_passes: Optional[int] = None,
-        fused: Optional[bool] = None,
+        fused: Union[None, bool, str] = None,
     ):
         super().__init__()
         self.fused = fused
+        self._no_fused_forward = self._no_fused_backward = False
         self.encoding = encoding
         self.mlp = mlp
         self.grad_out_scale = grad_out_scale
@@ -187,28 +190,24 @@ class NeuralFieldTrainer(nn.Module):
         code, act = _lib.dtype_code(st.flat_grad), _lib.ACTIVATION_CODE[mlp.activation]
         mlp_ptrs = (st.w_in.data_ptr(), _lib.ptr(st.b_in), _lib.ptr(st.w_hid), _lib.ptr(st.b_hid), st.w_out.data_ptr(), _lib.ptr(st.b_out))
         dims = (st.d_feat, st.d_hidden, st.d_out, st.depth)
-        use_fused = self.fused is not False and not self.backward_passes
-        if use_fused and st.b_in is not None:  # the fused backward is built for bias-free networks
-            if self.fused:
-                raise FieldUnsupported("bias-free networks only (backward)")
-            use_fused = False
+        fuse_fwd, fuse_bwd = self._fusion_plan(st)
         with torch.cuda.device(device):
             stream = _lib.stream_ptr(device)
             st.loss_sum.zero_()
             geometry = (launch.n, d_coord, st.n_feats, enc.num_levels, launch.res, launch.rows, launch.offsets, launch.primes, launch.scale)
             weights = (st.w_in, st.w_out, st.w_hid)
-            if use_fused:
+            # ---- forward: encoding, MLP, loss ----
+            if fuse_fwd:
                 try:
                     field_forward(launch, enc.embeddings.data, *weights, mlp.activation, enc.num_levels, feats_out=st.feats,
                                   target=targets, grad_out=st.grad_pred, loss_sum=st.loss_sum, grad_scale=scale,
                                   biases=(st.b_in, st.b_hid, st.b_out))  # fmt: skip
-                    field_backward(launch, st.feats, st.grad_pred, *weights, mlp.activation, enc.num_levels, st.table_grad, st.workspace)
                 except FieldUnsupported:
-                    if self.fused:
+                    if self.fused is True:
                         raise
-                    self.fused = use_fused = False  # take the separate operators from now on
-                    st.loss_sum.zero_()
-            if not use_fused:
+                    self._no_fused_forward = True  # nothing was launched: the separate operators from now on
+                    fuse_fwd = False
+            if not fuse_fwd:
                 _lib.check(
                     lib.th_hash_fwd(*launch.coord_args, enc.embeddings.data_ptr(), code, st.feats.data_ptr(), st.d_feat,
                                     *geometry, 0, enc.num_levels, stream),
@@ -224,6 +223,16 @@ class NeuralFieldTrainer(nn.Module):
                     _lib.check(lib.th_mse_grad(st.pred.data_ptr(), t.data_ptr(), st.grad_pred.data_ptr(), st.loss_sum.data_ptr(), n * st.d_out, scale, code, stream), "th_mse_grad")
                 else:
                     _lib.check(rc, "th_mlp_fwd_mse")
+            # ---- backward: MLP, then the encoding's table gradient into the flat buffer ----
+            if fuse_bwd:
+                try:
+                    field_backward(launch, st.feats, st.grad_pred, *weights, mlp.activation, enc.num_levels, st.table_grad, st.workspace)
+                except FieldUnsupported:
+                    if self.fused in (True, "backward"):
+                        raise
+                    self._no_fused_backward = True
+                    fuse_bwd = False
+            if not fuse_bwd:
                 _lib.check(
                     lib.th_mlp_bwd(st.feats.data_ptr(), st.d_feat, *mlp_ptrs, st.grad_pred.data_ptr(), st.d_out, st.grad_feats.data_ptr(),
                                    st.d_feat, None, None, None, None, None, None, st.workspace.data_ptr(), st.workspace.numel() * 4,
@@ -233,7 +242,7 @@ class NeuralFieldTrainer(nn.Module):
             # float32 sums over this rank's rows -> mean of the unscaled gradient, rounded into the flat buffer's tail
             _lib.check(lib.th_scale_cast(st.workspace.data_ptr(), st.mlp_grad.data_ptr(), st.mlp_grad.numel(), cast_scale, code, stream), "th_scale_cast")
             pending = PendingReduce(self.group, bucket_bytes=0)
-            if use_fused:
+            if fuse_bwd:
                 pending.start([st.flat_grad])
             else:
                 passes = [(0, enc.num_levels)] if not self.backward_passes else level_passes(launch.geo.rows, self.backward_passes)
@@ -251,6 +260,20 @@ class NeuralFieldTrainer(nn.Module):
                     self.eps, table_adam_scale, True, st.skipped)  # fmt: skip
         adam_update(st.mlp_flat, st.mlp_grad, st.mlp_m, st.mlp_v, self._steps, self.lr, self.betas, self.eps, mlp_adam_scale, False, st.skipped)
         return st.loss_sum / (n * st.d_out)
+
+    def _fusion_plan(self, st: "_DirectState") -> Tuple[bool, bool]:
+        r"""(fused forward?, fused backward?) for this step; see ``fused`` in the class docstring."""
+        mode = self.fused
+        if mode is False:
+            return False, False
+        want_fwd = mode is True
+        want_bwd = mode in (None, True, "backward")
+        if st.b_in is not None or self.backward_passes:
+            # the fused backward is built for bias-free networks; level-range passes need the separate encoding backward
+            if mode in (True, "backward"):
+                raise FieldUnsupported("the fused backward takes bias-free networks and one pass over all levels")
+            want_bwd = False
+        return want_fwd and not self._no_fused_forward, want_bwd and not self._no_fused_backward
 
     def _prepare(self, coords: Tensor) -> "_DirectState":
         st = self._state
