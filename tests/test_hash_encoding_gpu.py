@@ -97,6 +97,22 @@ def test_indices_fp16_coords_and_scale():
         assert torch.equal(w[:, lvl].cpu(), oracle.corner_weights(x.float(), 3, res[lvl]))
 
 
+@pytest.mark.parametrize("scale", [3.0, 0.7, 1000.0])
+def test_indices_with_a_scale_that_is_not_a_power_of_two(scale):
+    # The kernels divide the coordinate by `scale` (one float32 division) and then follow the CPU path, which
+    # is what the reference's tests do before calling its CPU function (tests/test_layers/test_hash_encoding.py:427-428):
+    # bit-exact against the oracle fed x / scale.  (The reference's Triton kernel folds 1 / scale into its first
+    # level multiplier instead and can land in the neighbouring cell on a cell boundary.)
+    g = torch.Generator().manual_seed(9)
+    x = torch.rand(5000, 3, generator=g) * scale
+    res, rows = [16, 23, 101, 512, 4096], [17**3, 24**3, 2**14, 2**19, 2**22]
+    idx, w = hash_corner_indices(x.cuda(), res, rows, scale=scale)
+    unit = x / scale  # float32 division, as in the kernels
+    for lvl in range(len(res)):
+        assert torch.equal(idx[:, lvl].cpu(), oracle.corner_indices(unit, oracle.PRIMES, 3, rows[lvl], res[lvl]))
+        assert torch.equal(w[:, lvl].cpu(), oracle.corner_weights(unit, 3, res[lvl]))
+
+
 @pytest.mark.parametrize("res", [16, 32, 512])
 @pytest.mark.parametrize("unique", [False, True])
 def test_indices_in_range(res, unique):
@@ -285,6 +301,25 @@ def test_backward_clustered_points(dtype, F):
     t = table.cuda().requires_grad_(True)
     hash_encoding(x.cuda(), t, None, None, T, lo, hi, L).backward(go.cuda())
     assert nerr(t.grad, want) <= (BWD_TOL_F32 if dtype == torch.float32 else 2e-2)
+
+
+def test_contention_configuration_on_its_own_table():
+    # benchmark configuration 4's table as it is - 16 levels x 4 float32 features, T = 2^22, 16..4096, 42 585 337
+    # rows (681 MB) - with 65 536 points drawn from its mixture of 8 Gaussians: forward within 1e-6 and table
+    # gradient within 1e-5 of the oracle (the size the oracle finishes in seconds; the full 2^22 points are
+    # covered by the size-independent properties below)
+    N, D, F, T, L, lo, hi = 65536, 3, 4, 2**22, 16, 16, 4096
+    x, table, go, kw = make_case(N, D, F, T, L, lo, hi, torch.float32, seed=17, clustered=True)
+    assert table.shape == (42_585_337, 4)
+    want = oracle.encode(x, table, **kw)
+    want_grad = oracle.encode_backward(x, go, table, **kw)
+    t = table.cuda().requires_grad_(True)
+    out = hash_encoding(x.cuda(), t, None, None, T, lo, hi, L)
+    assert nerr(out, want) <= FWD_TOL_F32
+    out.backward(go.cuda())
+    assert nerr(t.grad, want_grad) <= BWD_TOL_F32
+    # the gradient touches only rows the oracle touches
+    assert torch.equal((t.grad != 0).any(1).cpu(), (want_grad != 0).any(1))
 
 
 def test_backward_all_points_identical():

@@ -93,6 +93,34 @@ def test_forward_backward_against_oracle(dtype, rows, d_model, hidden, blocks, b
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows", [1024, 1300])
+def test_every_block_is_tight_without_an_activation(dtype, rows):
+    # Benchmark configuration 2's stack (8 blocks, d_model 128, hidden 64, no biases) with activation "none":
+    # no ReLU can switch on a one-ulp difference, so EVERY block's weight gradient - not only the last one's -
+    # must sit within the tight tolerance of the oracle that rounds where the kernels round.  A kernel that
+    # mis-addressed one block's gradient flush, or mixed up two blocks' weights, fails here by orders of magnitude.
+    d_model, hidden, blocks = 128, 64, 8
+    weights, biases = make_params(blocks, d_model // 2, hidden, False, dtype, seed=11)
+    weights = tuple((w.float() * 0.5).to(dtype) for w in weights)  # keep the linear stack's activations of order one
+    g = torch.Generator().manual_seed(rows)
+    x = torch.randn(rows, d_model, generator=g).to(dtype)
+    go = torch.randn(rows, d_model, generator=g).to(dtype)
+    wc = to_cuda(weights)
+    y = reversible_mlp_forward(x.cuda(), wc, (None,) * 4, "none")
+    y_r, _, _, _ = oracle.forward_backward_storage_rounded(x, weights, biases, go, "none")
+    assert nerr(y, y_r) <= 2 * TIGHT[dtype]
+    got = reversible_mlp_backward(y, go.cuda(), wc, (None,) * 4, "none", reconstruct=True)
+    _, dx_r, grads_r, xrec_r = oracle.forward_backward_storage_rounded(x, weights, biases, go, "none", y_saved=y.cpu())
+    assert nerr(got.dx, dx_r) <= 5 * TIGHT[dtype], nerr(got.dx, dx_r)
+    assert nerr(got.x_reconstructed, xrec_r) <= 5 * TIGHT[dtype]
+    for name, want, have in zip(("dw_f1", "dw_f2", "dw_g1", "dw_g2"), grads_r[:4], got[1:5]):
+        per_block = want.shape[0] // blocks
+        for b in range(blocks):
+            err = nerr(have[b * per_block : (b + 1) * per_block], want[b * per_block : (b + 1) * per_block])
+            assert err <= 5 * TIGHT[dtype], f"{name}, block {b}: {err}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_autograd_function_against_float32_autograd(dtype):
     # through the autograd.Function, against torch autograd with stored activations (float32)
     rows, d_model, hidden, blocks = 4096, 128, 64, 8
