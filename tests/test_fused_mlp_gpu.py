@@ -314,6 +314,46 @@ def test_tensor_core_kernels_never_timed_out():
     assert _lib.lib().th_mlp_tma_available() == 1
 
 
+@pytest.mark.parametrize("activation,bias", [("relu", True), ("silu", True), ("relu2", False), ("silu", False)])
+def test_biased_and_pre_activation_backward_run_on_the_tensor_core_kernel(activation, bias):
+    # The reference's module always has biases (fully_fused_mlp/module.py:22-37) and offers SiLU and ReLU^2:
+    # their backward passes run on the tcgen05 kernel too (bias gradients through an MMA with a tile of ones,
+    # activation derivatives from a recomputed pre-activation), not on the mma.sync fall-back.  The kernel
+    # names come from the profiler; the values are held to the oracle as everywhere else.
+    from torch.profiler import ProfilerActivity, profile
+
+    dtype, rows, d_in, d_hid, d_out, depth = torch.float16, 3000, 32, 64, 16, 3
+    params = make_params(d_in, d_hid, d_out, depth, dtype, bias=bias, seed=7)
+    p = [params[k] for k in ("w_in", "b_in", "w_out", "b_out", "w_hid", "b_hid")]
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(1, rows, d_in, generator=g).to(dtype)
+    go = (torch.randn(1, rows, d_out, generator=g) * 0.1).to(dtype)
+    leaves = [None if t is None else t.cuda().requires_grad_(True) for t in p]
+    xc = x.cuda().requires_grad_(True)
+    y = fully_fused_mlp(xc, *leaves, activation=activation)
+    torch.cuda.synchronize()
+    try:
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            y.backward(go.cuda())
+            torch.cuda.synchronize()
+        names = [e.key for e in prof.key_averages()]
+    except Exception as exc:  # noqa: BLE001  (no CUPTI on this machine: the numerical check below still runs)
+        names = None
+        if xc.grad is None:
+            y.backward(go.cuda())
+        print(f"profiler unavailable: {exc}")
+    if names is not None:
+        assert any("mlp_bwd_tc_kernel" in n for n in names), names
+        assert not any("mlp_bwd_kernel<" in n for n in names), names
+    ref = oracle.forward_backward_storage_rounded(x, *p, go.float(), activation=activation)
+    grad = lambda t: None if t is None else t.grad  # noqa: E731
+    got = (y, xc.grad, *(grad(t) for t in leaves))
+    for name, want, have in zip(("y", "dx", "dw_in", "db_in", "dw_out", "db_out", "dw_hid", "db_hid"), ref, got):
+        assert (want is None) == (have is None), name
+        if want is not None and name != "dx":
+            assert nerr(have, want) <= 1e-2, f"{name}: {nerr(have, want)}"
+
+
 def test_mma_sync_kernels_still_pass_when_selected():
     # TH_MLP_LEGACY=1 routes every call to the mma.sync kernels (the path that also serves biased
     # backward passes and SiLU / ReLU^2); rerun the shape tests that way in a fresh process

@@ -368,12 +368,58 @@ mlp_fwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
 }
 
 // ---- backward ----------------------------------------------------------------------------------
-template <typename T, int ACT, int MINB>
+//
+// Biases and activations that need the pre-activation (SiLU, ReLU^2) stay on the tensor cores:
+//   * bias gradient of layer l = column sums of dz_l over the tile's rows = dz_l^T . ONES, one more small
+//     MMA per step (A = the dz tile MN-major as for wgrad, B = a tile of ones, N = 16) into 16 TMEM columns
+//     per layer that live as long as the weight-gradient accumulators and are flushed with them;
+//   * SiLU' and ReLU^2' want z_{l-1}, which nobody kept: the step that needs it issues the layer's forward
+//     GEMM again (act[l-1] . W_{l-1}^T, four MMAs) into a second accumulator, and the epilogue reads dy and
+//     z side by side, rounds z to the storage dtype as the forward pass did (reference: activation
+//     derivatives are taken at the dtype-rounded pre-activation, fully_fused_mlp/kernel.py:278-281) and
+//     applies the derivative.  The tensor pipe has the room; shared memory does not.
+
+// dz of the layer below from dy (accumulator) and the recomputed pre-activation (second accumulator)
+template <typename T, int ACT, bool BIAS>
+__device__ __forceinline__ void dz_epilogue_preact(uint32_t taddr_dy, uint32_t taddr_z, const Seat &seat, int pad, const float *bias,
+                                                   unsigned char *dz_tile) {
+    const int n = pad / kGroups, first = seat.group * (n / 8);
+    const uint32_t dz_row = smem_addr(dz_tile) + seat.row * 128, row_swizzle = (seat.row & 7) << 4;
+    for (int u = 0; u < n / 8; ++u) {
+        uint32_t dy[8], zz[8];
+        tmem_ld8(taddr_dy + seat.group * n + 8 * u, dy);
+        tmem_ld8(taddr_z + seat.group * n + 8 * u, zz);
+        tmem_ld_wait();
+        float g[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            float z = __uint_as_float(zz[k]);
+            if constexpr (BIAS) z += bias[8 * (first + u) + k];
+            z = to_float<T>(from_float<T>(z));  // the forward pass stored z rounded
+            g[k] = activate_grad(ACT, z, __uint_as_float(dy[k]));
+        }
+        st_shared_16(dz_row + (((first + u) << 4) ^ row_swizzle),
+                     make_uint4(pack_pair<T>(g[0], g[1]), pack_pair<T>(g[2], g[3]), pack_pair<T>(g[4], g[5]), pack_pair<T>(g[6], g[7])));
+    }
+}
+
+// Column 0 of a bias-gradient accumulator (M = 64 layout, see flush_dw) -> float32 sums
+__device__ __forceinline__ void flush_db(uint32_t taddr, float *dst, int out_dim) {
+    uint32_t raw[8];
+    tmem_ld8(taddr, raw);
+    tmem_ld_wait();
+    const int lane = threadIdx.x & 31;
+    const int m = 16 * ((threadIdx.x >> 5) & 3) + lane;
+    if (threadIdx.x < 128 && lane < 16 && m < out_dim) atomicAdd(dst + m, __uint_as_float(raw[0]));
+}
+
+template <typename T, int ACT, int MINB, bool BIAS>
 __global__ void __launch_bounds__(kTcThreads, MINB)
 mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ WeightMaps maps, const int use_tma,
                   const T *__restrict__ x, long long x_stride,
                   const T *__restrict__ go, long long go_stride, T *__restrict__ gx, long long gx_stride,
                   float *__restrict__ workspace, long long n_rows, int x_vec, int go_vec, int gx_vec) {
+    constexpr bool kPreact = ACT == TH_ACT_SILU || ACT == TH_ACT_RELU2;
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint32_t tmem_holder;
@@ -387,6 +433,15 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
     // operand tiles start out as zeros: columns a layer does not use are still read as MMA rows
     for (int e = threadIdx.x; e < (P.act_tiles + P.dz_tiles) * kTileBytes / 16; e += kTcThreads)
         reinterpret_cast<uint4 *>(smem)[e] = make_uint4(0, 0, 0, 0);
+    unsigned char *ones_tile = smem + (P.act_tiles + P.dz_tiles) * kTileBytes;
+    if constexpr (BIAS) {
+        // 128 rows x 16 columns of ones (logical chunks 0 and 1 of every row), zeros elsewhere
+        const uint32_t one2 = pack_pair<T>(1.f, 1.f);
+        for (int e = threadIdx.x; e < kTileBytes / 16; e += kTcThreads) {
+            const int r = e >> 3, c = (e & 7) ^ (r & 7);  // physical chunk e & 7 of row r holds logical chunk c
+            reinterpret_cast<uint4 *>(ones_tile)[e] = c < 2 ? make_uint4(one2, one2, one2, one2) : make_uint4(0, 0, 0, 0);
+        }
+    }
     stage_biases<T>(smem, P, s, p);
     bool weights_ok = true;
     if (use_tma) weights_ok = tma_stage_weights(smem, P, s, maps, &wbar);
@@ -398,6 +453,7 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
     }
     __syncthreads();
     const uint32_t bar = smem_addr(&mbar);
+    const float *bias = reinterpret_cast<const float *>(smem + P.bias_offset);
     unsigned char *dz_tiles = smem + P.act_tiles * kTileBytes;
     const Seat seat;
     const uint32_t taddr = tmem + seat.lane_base;
@@ -406,6 +462,7 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
     const long long n_tiles = (n_rows + kTileRows - 1) / kTileRows;
     auto act_tile = [&](int l) { return smem + l * kTileBytes; };
     auto dw_col = [&](int l) { return kAccCols + (l == 0 ? 0 : s.ki + (l - 1) * s.h); };
+    auto db_col = [&](int l) { return P.db_col + 16 * l; };
 
     // With one CTA per SM (MINB == 1: shared memory bound, registers to spare) the next tile's inputs
     // are fetched into registers while the current tile computes; with two CTAs per SM the other
@@ -450,7 +507,7 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
             if (!ok) {
                 g_tc_status = 1;
             } else {
-                hidden_epilogue<T, ACT, false>(taddr, seat, s.h, nullptr, act_tile(l + 1));
+                hidden_epilogue<T, ACT, BIAS>(taddr, seat, s.h, bias + l * kMaxDim, act_tile(l + 1));
             }
             fence_async_smem();
             tc_fence_before();
@@ -474,9 +531,17 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
                 if (need_dgrad)
                     issue_gemm(leader, tmem, smem_addr(dz), 32, smem_addr(weight_tile(smem, P, s, l)), 2048, out_pad / 16,
                                instr_desc(128, in_pad, bf16, 0, 1), false);
+                // the pre-activation of the layer below, for its activation's derivative
+                if (kPreact && l > 0)
+                    issue_gemm(leader, tmem + P.z_col, smem_addr(act_tile(l - 1)), 32, smem_addr(weight_tile(smem, P, s, l - 1)), 32,
+                               (l == 1 ? s.ki : s.h) / 16, instr_desc(128, s.h, bf16, 0, 0), false);
                 // wgrad: DW_l[out x in] += DZ^T . ACT_l over the tile's 128 rows (both operands MN-major)
                 issue_gemm(leader, tmem + dw_col(l), smem_addr(dz), 2048, smem_addr(act_tile(l)), 2048, kTileRows / 16,
                            instr_desc(64, in_pad, bf16, 1, 1), !first_tile);
+                // bias gradient: DB_l[out x 16] += DZ^T . ONES (every column holds the column sums of dz)
+                if (BIAS)
+                    issue_gemm(leader, tmem + db_col(l), smem_addr(dz), 2048, smem_addr(ones_tile), 2048, kTileRows / 16,
+                               instr_desc(64, 16, bf16, 1, 1), !first_tile);
                 if (leader) mma_commit(bar);
                 __syncwarp();
             }
@@ -485,7 +550,10 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
                 g_tc_status = 1;
             } else if (l > 0) {
                 // in_pad == s.h here: the layer below produced ACT_l
-                dz_epilogue<T, ACT>(taddr, seat, in_pad, act_tile(l), dz_tiles + (buf ^ 1) * kTileBytes);
+                if constexpr (kPreact)
+                    dz_epilogue_preact<T, ACT, BIAS>(taddr, taddr + P.z_col, seat, in_pad, bias + (l - 1) * kMaxDim, dz_tiles + (buf ^ 1) * kTileBytes);
+                else
+                    dz_epilogue<T, ACT>(taddr, seat, in_pad, act_tile(l), dz_tiles + (buf ^ 1) * kTileBytes);
             } else if (gx != nullptr) {
                 const bool live = row0 + seat.row < n_rows;
                 dx_epilogue<T>(taddr, seat, in_pad, gx + (live ? row0 + seat.row : 0) * gx_stride, s.d_in, live, gx_vec);
@@ -500,7 +568,7 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
         first_tile = false;
     }
 
-    // ---- flush the weight gradients this CTA accumulated in TMEM ----
+    // ---- flush the weight (and bias) gradients this CTA accumulated in TMEM ----
     if (!abort_flag && !first_tile) {
         tc_fence_after();
         const MlpGradWorkspace W = grad_workspace_layout(s, workspace);
@@ -509,6 +577,10 @@ mlp_bwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
             const int in_dim = l == 0 ? s.d_in : s.d_hid, out_dim = l == s.depth ? s.d_out : s.d_hid;
             float *dst = W.base + (l == 0 ? W.w_in : (l == s.depth ? W.w_out : W.w_hid + (l - 1) * s.d_hid * s.d_hid));
             flush_dw(taddr + dw_col(l), seat, in_pad, dst, out_dim, in_dim);
+            if constexpr (BIAS) {
+                float *bdst = W.base + (l == 0 ? W.b_in : (l == s.depth ? W.b_out : W.b_hid + (l - 1) * s.d_hid));
+                flush_db(taddr + db_col(l), bdst, out_dim);
+            }
         }
     }
     cta_teardown(tmem, P.tmem_cols);
@@ -908,10 +980,11 @@ int launch_bwd_pipe(const MlpShape &s, const MlpParams &p, const void *x, int64_
     return launch_status("mlp_bwd_pipe_kernel launch");
 }
 
-template <typename T, int ACT>
+template <typename T, int ACT, bool BIAS>
 int launch_bwd_t(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, const void *go, int64_t go_stride,
                  void *gx, int64_t gx_stride, float *workspace, int64_t rows, cudaStream_t stream) {
-    {
+    // the issuer-warp kernel is built for bias-free networks whose activation derivative needs no pre-activation
+    if constexpr (!BIAS && (ACT == TH_ACT_RELU || ACT == TH_ACT_NONE)) {
         const int rc = launch_bwd_pipe<T, ACT>(s, p, x, x_stride, go, go_stride, gx, gx_stride, workspace, rows, stream);
         if (rc != kTcNotApplicable) return rc;
     }
@@ -921,7 +994,7 @@ int launch_bwd_t(const MlpShape &s, const MlpParams &p, const void *x, int64_t x
     const int smem = occupancy_plan(P, &ctas);
     if (ctas < 1) return kTcNotApplicable;
     // one CTA per SM (shared memory bound): let it keep its prefetched tiles in registers
-    auto kernel = ctas >= 2 ? mlp_bwd_tc_kernel<T, ACT, 2> : mlp_bwd_tc_kernel<T, ACT, 1>;
+    auto kernel = ctas >= 2 ? mlp_bwd_tc_kernel<T, ACT, 2, BIAS> : mlp_bwd_tc_kernel<T, ACT, 1, BIAS>;
     if (int rc = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
                              "cudaFuncSetAttribute(mlp_bwd_tc_kernel)")) return rc;
     const long long tiles = (rows + kTileRows - 1) / kTileRows;
@@ -938,9 +1011,16 @@ int launch_bwd_t(const MlpShape &s, const MlpParams &p, const void *x, int64_t x
 template <typename T>
 int launch_bwd(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, const void *go, int64_t go_stride,
                void *gx, int64_t gx_stride, float *workspace, int64_t rows, cudaStream_t stream) {
-    return s.act == TH_ACT_RELU
-               ? launch_bwd_t<T, TH_ACT_RELU>(s, p, x, x_stride, go, go_stride, gx, gx_stride, workspace, rows, stream)
-               : launch_bwd_t<T, TH_ACT_NONE>(s, p, x, x_stride, go, go_stride, gx, gx_stride, workspace, rows, stream);
+#define TH_BWD_ACT(A)                                                                                                   \
+    (s.has_bias ? launch_bwd_t<T, A, true>(s, p, x, x_stride, go, go_stride, gx, gx_stride, workspace, rows, stream)    \
+                : launch_bwd_t<T, A, false>(s, p, x, x_stride, go, go_stride, gx, gx_stride, workspace, rows, stream))
+    switch (s.act) {
+        case TH_ACT_RELU: return TH_BWD_ACT(TH_ACT_RELU);
+        case TH_ACT_SILU: return TH_BWD_ACT(TH_ACT_SILU);
+        case TH_ACT_RELU2: return TH_BWD_ACT(TH_ACT_RELU2);
+        default: return TH_BWD_ACT(TH_ACT_NONE);
+    }
+#undef TH_BWD_ACT
 }
 
 // ---- forward with the fused MSE epilogue: only the multi-slot kernel has it ----
@@ -995,8 +1075,6 @@ int mlp_bwd_tc(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_s
                void *gx, int64_t gx_stride, float *workspace, int64_t rows, int dtype, cudaStream_t stream) {
     if (tc_disabled() || rows <= 0) return kTcNotApplicable;
     if (s.h != 16 && s.h != 32 && s.h != 64) return kTcNotApplicable;
-    // bias gradients and activations that need the pre-activation stay on the mma.sync kernels
-    if (s.has_bias || (s.act != TH_ACT_RELU && s.act != TH_ACT_NONE)) return kTcNotApplicable;
     switch (dtype) {
         case TH_F16: return launch_bwd<__half>(s, p, x, x_stride, go, go_stride, gx, gx_stride, workspace, rows, stream);
         case TH_BF16: return launch_bwd<__nv_bfloat16>(s, p, x, x_stride, go, go_stride, gx, gx_stride, workspace, rows, stream);

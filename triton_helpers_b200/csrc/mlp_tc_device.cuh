@@ -22,6 +22,9 @@ constexpr int kAccCols = 64;  // TMEM columns of the forward / dgrad accumulator
 struct TcPlan {
     int act_tiles;      // operand tiles for activations (2 forward, depth + 1 backward)
     int dz_tiles;       // 0 forward, 2 backward
+    int ones_tile;      // backward with biases: one tile of ones, the B operand that turns dz into its column sums
+    int db_col;         // backward with biases: first TMEM column of the bias-gradient accumulators (16 per layer)
+    int z_col;          // backward with SiLU / ReLU^2: TMEM column of the recomputed pre-activation (64 columns)
     int w_offset[3];    // byte offsets of W_in, W_hid[0], W_out tiles (after the activation / dz tiles)
     int w_hid_each;
     int bias_offset;    // fp32 [(depth + 1)][64]
@@ -33,7 +36,8 @@ __host__ __device__ inline TcPlan tc_plan(const MlpShape &s, bool backward, int 
     TcPlan p{};
     p.act_tiles = backward ? s.depth + 1 : forward_tiles;  // forward: two tiles per row tile in flight, alternating, so the next input can stream in
     p.dz_tiles = backward ? 2 : 0;
-    int off = (p.act_tiles + p.dz_tiles) * kTileBytes;
+    p.ones_tile = backward && s.has_bias ? 1 : 0;
+    int off = (p.act_tiles + p.dz_tiles + p.ones_tile) * kTileBytes;
     p.w_offset[0] = off;
     off += s.h * 128;
     p.w_offset[1] = off;
@@ -46,6 +50,10 @@ __host__ __device__ inline TcPlan tc_plan(const MlpShape &s, bool backward, int 
     p.total = off;
     int cols = kAccCols;
     if (backward) cols += s.ki + s.depth * s.h;  // one accumulator of in_pad columns per layer
+    p.db_col = cols;
+    if (backward && s.has_bias) cols += 16 * (s.depth + 1);
+    p.z_col = cols;
+    if (backward && (s.act == TH_ACT_SILU || s.act == TH_ACT_RELU2)) cols += kAccCols;
     int alloc = 32;
     while (alloc < cols) alloc <<= 1;
     p.tmem_cols = alloc;
