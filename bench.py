@@ -529,17 +529,15 @@ def health(world, device, losses, skipped):
     from triton_helpers_b200 import _lib
 
     lib = _lib.lib()
-    bad = 0
-    bad |= 1 if any(not math.isfinite(v) for v in losses) else 0
-    bad |= 2 if skipped else 0
-    bad |= 4 if (lib.th_mlp_tc_status() != 0 or lib.th_rev_tc_status() != 0) else 0
-    flag = torch.tensor([bad], dtype=torch.int32, device=device)
+    flags = torch.tensor([int(any(not math.isfinite(v) for v in losses)), int(bool(skipped)),
+                          int(lib.th_mlp_tc_status() != 0 or lib.th_rev_tc_status() != 0 or lib.th_hash_status() != 0)],
+                         dtype=torch.int32, device=device)  # fmt: skip
     if world > 1:
-        dist.all_reduce(flag, op=dist.ReduceOp.BOR)
-    bad = int(flag)
-    if bad:
-        reasons = [text for bit, text in ((1, "a loss is not finite"), (2, "Adam skipped non-finite gradients"),
-                                          (4, "a tensor-core kernel gave up on a wait")) if bad & bit]  # fmt: skip
+        dist.all_reduce(flags, op=dist.ReduceOp.MAX)  # NCCL has no bitwise reductions: one 0/1 flag per reason
+    bad = [bool(v) for v in flags.tolist()]
+    if any(bad):
+        reasons = [text for hit, text in zip(bad, ("a loss is not finite", "Adam skipped non-finite gradients",
+                                                   "a tensor-core or encoding kernel gave up on a wait")) if hit]  # fmt: skip
         raise SystemExit(f"bench.py: invalid run on at least one rank: {'; '.join(reasons)} (losses here: {losses})")
 
 

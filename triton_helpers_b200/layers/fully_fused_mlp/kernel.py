@@ -12,10 +12,13 @@ Differences a caller can observe:
   mantissa, float32 accumulation) for the tensor cores and the results are returned in float32;
   values beyond the float16 range (|v| > 65504) overflow, which TF32 would not.  As in the
   reference, a float32 backward pass is refused for depth >= 4 (reference :576).
-* ``fp16_acc`` is accepted and ignored: accumulation is always float32.
+* ``fp16_acc=True`` is accepted (the reference's callers and benchmarks pass it) but changes nothing:
+  accumulation is always float32, which is at least as accurate as what was asked for.  The first
+  such call emits a ``UserWarning`` saying so.
 * biases may be ``None`` (all of them) for a bias-free network; the reference requires tensors.
 * the Triton device functions the reference re-exports (``feedforward`` ...) do not exist.
 """
+import warnings
 from typing import Final, Optional
 
 import torch
@@ -28,6 +31,16 @@ from ...ops import ensure_str
 # Above this size the weights no longer stay on chip (reference :13-14)
 FULLY_FUSED_MAX_DIM: Final = 64
 ACTIVATIONS: Final = ("relu", "relu2", "silu", "none")
+
+
+_FP16_ACC_WARNED = False
+
+
+def _warn_fp16_acc() -> None:
+    global _FP16_ACC_WARNED
+    if not _FP16_ACC_WARNED:
+        _FP16_ACC_WARNED = True
+        warnings.warn("fp16_acc=True is accepted for compatibility; these kernels always accumulate in float32", UserWarning, stacklevel=3)
 
 
 def _rows_view(t: Tensor) -> Tensor:
@@ -86,6 +99,8 @@ class _fully_fused_mlp(Function):
             depth = 1
             w_hid = b_hid = None
         assert activation in ACTIVATIONS, f"Invalid activation function: {activation}"
+        if fp16_acc:
+            _warn_fp16_acc()
         has_bias = b_in is not None
         assert (b_out is not None) == has_bias and (depth == 1 or (b_hid is not None) == has_bias), (
             "Biases must be given for every layer or for none"

@@ -110,7 +110,8 @@ def reversible_mlp_backward(
     x_rec = torch.empty_like(dx) if reconstruct else None
     dws = tuple(torch.empty_like(w) for w in weights)
     dbs = tuple(None if b is None else torch.empty_like(b) for b in biases)
-    ws_bytes = _lib.lib().th_rev_workspace_bytes(rows, d_model, d_hidden, blocks)
+    with torch.cuda.device(device):  # the size depends on the SM count of the tensors' device, which must be current
+        ws_bytes = _lib.lib().th_rev_workspace_bytes(rows, d_model, d_hidden, blocks)
     workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=device)
     stride = lambda t: t.stride(0) if t.shape[0] > 1 else d_model  # noqa: E731
     with torch.cuda.device(device):
