@@ -370,6 +370,22 @@ def test_mma_sync_kernels_still_pass_when_selected():
     assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-2000:]
 
 
+def test_pipelined_backward_still_passes_when_the_shared_accumulator_kernel_is_off():
+    # TH_MLP_NO_SLOTS=1 sends bias-free ReLU / linear backward passes to the one-tile-chain pipelined kernel,
+    # which otherwise only serves networks too deep for several row tiles per SM
+    import os
+    import subprocess
+    import sys
+
+    if os.environ.get("TH_MLP_NO_SLOTS") == "1" or os.environ.get("TH_MLP_LEGACY") == "1":
+        pytest.skip("already running without the shared-accumulator kernel")
+    env = dict(os.environ, TH_MLP_NO_SLOTS="1")
+    cmd = [sys.executable, "-m", "pytest", __file__, "-q", "-x", "-m", "gpu", "-k",
+           "reference_shapes or shapes_against_oracle or empty_batch"]  # fmt: skip
+    done = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-2000:]
+
+
 # ---- forward fused with the squared-error loss -----------------------------------------------------
 
 

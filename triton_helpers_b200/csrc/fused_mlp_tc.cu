@@ -638,7 +638,7 @@ mlp_bwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
         asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars.acc_full)), "r"(1u) : "memory");
         asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars.wgrad_done[0])), "r"(1u) : "memory");
         asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars.wgrad_done[1])), "r"(1u) : "memory");
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars.ready)), "r"(static_cast<uint32_t>(kTcThreads)) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars.ready)), "r"(static_cast<uint32_t>(kTcThreads / 32)) : "memory");
     }
     // operand tiles start out as zeros: columns a layer does not use are still read as MMA rows
     for (int e = threadIdx.x; e < (P.act_tiles + P.dz_tiles) * kTileBytes / 16; e += blockDim.x)
@@ -788,7 +788,8 @@ mlp_bwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
         auto publish = [&]() {
             fence_async_smem();
             tc_fence_before();
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ready_bar) : "memory");
+            __syncwarp();  // one arrival per warp: arrivals on one mbarrier are serialised, a hundred of them cost a microsecond
+            if ((threadIdx.x & 31) == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ready_bar) : "memory");
         };
         for (long long k = 0; k < n_mine; ++k) {
             const long long row0 = (first_tile + k * gridDim.x) * kTileRows;
@@ -861,6 +862,351 @@ mlp_bwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
     __syncthreads();
     if (warp == 8)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(static_cast<uint32_t>(P.tmem_cols)) : "memory");
+}
+
+// ---- backward, several row tiles per CTA -------------------------------------------------------------
+//
+// The two kernels above keep at most two row tiles per SM in flight (one per CTA), because every CTA holds
+// its own weight-gradient accumulators (ki + depth x 64 TMEM columns) and depth + 3 operand tiles, and each
+// tile is a chain of 2 depth + 1 short steps that are mostly latency.  Here ONE CTA per SM runs S independent
+// SLOTS of 128 threads (thread = tile row = TMEM lane) plus one WGRAD warp:
+//   * a slot's warp 0 issues the slot's recompute and dgrad MMAs into the slot's own 64 accumulator columns
+//     (as in the forward kernel), so that chain never leaves the slot;
+//   * the wgrad warp issues the weight-gradient MMAs of every slot.  MMAs of one thread execute in order, so
+//     all slots accumulate into ONE shared set of TMEM columns instead of one set per tile in flight;
+//   * dz of layer l - 1 is written in place over the parked input of layer l once both MMAs that read it have
+//     finished, so a slot needs depth + 2 operand tiles;
+//   * when features and output gradient are at most 32 wide, the output-gradient tile of a slot lives in
+//     the logical chunks 4..7 of its feature tile (which uses chunks 0..3): depth + 1 tiles per slot.  The
+//     output layer's wgrad then reads the whole feature tile as its A operand, and the real gradient rows
+//     sit at rows 32.. of that layer's accumulator (rows 0..31 are products nobody reads).
+// Per slot three mbarriers: `ready` (one arrival: the operands of the slot's next backward step are in place),
+// `acc` (the slot's own MMAs of the step are done) and `wdone` (the step's wgrad is done).  The wgrad warp
+// polls all `ready` barriers at once, one lane per slot, without blocking; a slot's warp 0 polls `acc` and
+// `wdone`, its other warps park at the slot's named barrier.  Every wait is bounded by the global timer and
+// watches the CTA's abort flag; after an abort everybody keeps the same barrier sequence without doing work.
+
+struct BwdSlotPlan {
+    int packed;          // the output gradient shares the feature tile
+    int tiles_per_slot;
+    int slots;
+    int weights;         // byte offset of the weight tiles
+    int total;           // dynamic shared memory without the alignment slack
+    int tmem_cols;
+    TcPlan w;            // weight offsets relative to `weights`
+};
+
+inline BwdSlotPlan bwd_slot_plan(const MlpShape &s, int slots) {
+    BwdSlotPlan b{};
+    b.packed = (s.ki <= 32 && s.no <= 32) ? 1 : 0;
+    b.tiles_per_slot = s.depth + 1 + (b.packed ? 0 : 1);
+    b.slots = slots;
+    b.weights = slots * b.tiles_per_slot * kTileBytes;
+    b.w = tc_plan(s, false, 0);
+    b.total = b.weights + b.w.total;
+    const int cols = slots * kAccCols + s.ki + s.depth * s.h;
+    int alloc = 32;
+    while (alloc < cols) alloc <<= 1;
+    b.tmem_cols = alloc;
+    return b;
+}
+
+struct BwdSlotBarriers {
+    unsigned long long ready[kMaxSlots];
+    unsigned long long acc[kMaxSlots];
+    unsigned long long wdone[kMaxSlots];
+};
+
+// What the issuing warps need for one step of a tile, worked out once per CTA: both issue paths are on the
+// critical chain of every tile, and each address or descriptor computed there is paid 2 depth + 1 times per tile.
+struct __align__(16) SlotStep {
+    uint32_t a_off;    // the slot's own GEMM: A operand, relative to the slot's first tile
+    uint32_t b_addr;   //   B operand (a weight tile)
+    uint32_t idesc;    //   instruction descriptor; 0 = the step has no GEMM of its own
+    uint32_t k_steps;  //   bits 0..7: K steps of 16; bit 8: B is read MN-major
+    uint32_t wa_off;   // weight gradient: A operand (dz, MN-major), relative to the slot's first tile
+    uint32_t wb_off;   //   B operand (the layer's input, MN-major)
+    uint32_t widesc;   //   instruction descriptor
+    uint32_t dw_col;   //   accumulator column
+};
+constexpr int kMaxSlotSteps = 16;  // 2 depth + 1 steps; deeper networks do not fit two slots anyway
+
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                 : "=r"(done)
+                 : "r"(bar), "r"(parity)
+                 : "memory");
+    return done != 0;
+}
+
+template <typename T, int ACT, int S>
+__global__ void __launch_bounds__(128 * S + 32, 1)
+mlp_bwd_slots_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ WeightMaps maps, const int packed,
+                     const T *__restrict__ x, long long x_stride, const T *__restrict__ go, long long go_stride,
+                     T *__restrict__ gx, long long gx_stride, float *__restrict__ workspace, long long n_rows, int gx_vec) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ uint32_t tmem_holder;
+    __shared__ int abort_flag;
+    __shared__ __align__(8) unsigned long long wbar;
+    __shared__ __align__(8) BwdSlotBarriers bars;
+    __shared__ SlotStep steps[kMaxSlotSteps];
+    constexpr int bf16 = std::is_same<T, __half>::value ? 0 : 1;
+    const int d = s.depth;
+    const int tiles_per_slot = d + 1 + (packed ? 0 : 1);
+    const int weights_off = S * tiles_per_slot * kTileBytes;
+    const TcPlan WP = tc_plan(s, false, 0);
+    unsigned char *wsmem = smem + weights_off;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool is_wgrad_warp = warp == 4 * S;
+    int dw_cols = S * kAccCols + s.ki + d * s.h, tmem_cols = 32;
+    while (tmem_cols < dw_cols) tmem_cols <<= 1;
+    volatile int *abort_now = &abort_flag;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int i = 0; i < S; ++i) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars.ready[i])), "r"(1u) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars.acc[i])), "r"(1u) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars.wdone[i])), "r"(1u) : "memory");
+        }
+    }
+    // operand tiles start out as zeros: columns a layer does not use are still read as MMA rows
+    for (int e = threadIdx.x; e < weights_off / 16; e += blockDim.x) reinterpret_cast<uint4 *>(smem)[e] = make_uint4(0, 0, 0, 0);
+    fence_async_smem();
+    const bool weights_ok = tma_stage_weights(wsmem, WP, s, maps, &wbar);  // contains the barrier that publishes the inits
+    if (is_wgrad_warp) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_holder)),
+                     "r"(static_cast<uint32_t>(tmem_cols))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (!weights_ok) {
+        abort_flag = 1;
+        g_tc_status = 1;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_holder;
+
+    const long long n_tiles = (n_rows + kTileRows - 1) / kTileRows;
+    const long long first_tile = blockIdx.x, tile_stride = gridDim.x;
+    const long long n_mine = first_tile < n_tiles ? (n_tiles - first_tile + tile_stride - 1) / tile_stride : 0;
+    const uint32_t smem_base = smem_addr(smem);
+    const uint32_t slot_bytes = static_cast<uint32_t>(tiles_per_slot) * kTileBytes;
+    // the output gradient of a slot: its own tile, or logical chunks 4.. of the slot's feature tile
+    const uint32_t go_off = packed ? 64u : static_cast<uint32_t>(d + 1) * kTileBytes;
+    const int go_chunk0 = packed ? 4 : 0;
+    const int n_steps = 2 * d + 1;  // steps 0 .. d - 1 recompute layers 0 .. d - 1, step j >= d is the backward step of layer 2 d - j
+    auto dw_col = [&](int l) { return S * kAccCols + (l == 0 ? 0 : s.ki + (l - 1) * s.h); };
+    if (static_cast<int>(threadIdx.x) < n_steps) {
+        const int j = threadIdx.x;
+        SlotStep st{};
+        if (j < d) {
+            st.a_off = static_cast<uint32_t>(j) * kTileBytes;
+            st.b_addr = smem_addr(weight_tile(wsmem, WP, s, j));
+            st.idesc = instr_desc(128, s.h, bf16, 0, 0);
+            st.k_steps = static_cast<uint32_t>((j == 0 ? s.ki : s.h) / 16);
+        } else {
+            const int l = 2 * d - j;
+            const int in_pad = l == 0 ? s.ki : s.h, out_pad = l == d ? s.no : s.h;
+            const uint32_t dz_off = l == d ? go_off : static_cast<uint32_t>(l + 1) * kTileBytes;
+            if (l > 0 || gx != nullptr) {
+                st.a_off = dz_off;
+                st.b_addr = smem_addr(weight_tile(wsmem, WP, s, l));
+                st.idesc = instr_desc(128, in_pad, bf16, 0, 1);
+                st.k_steps = static_cast<uint32_t>(out_pad / 16) | 256u;
+            }
+            st.wa_off = (l == d && packed) ? 0u : dz_off;  // packed output gradient: the whole feature tile is the A operand
+            st.wb_off = static_cast<uint32_t>(l) * kTileBytes;
+            st.widesc = instr_desc(64, in_pad, bf16, 1, 1);
+            st.dw_col = static_cast<uint32_t>(dw_col(l));
+        }
+        steps[j] = st;
+    }
+    __syncthreads();
+
+    if (is_wgrad_warp) {
+        // ================= weight gradients of every slot =================
+        // lane i < S keeps slot i's state: its next backward step, the tiles it still has, the parity to wait for
+        int my_step = d;
+        long long my_tiles = lane < S && lane < n_mine ? (n_mine - lane + S - 1) / S : 0;
+        uint32_t my_parity = 0, dw_started = 0;
+        const uint32_t my_bar = smem_addr(&bars.ready[lane < S ? lane : 0]);
+        unsigned long long deadline = 0;
+        unsigned idle = 0;
+        const bool leader = elect_one();  // the same lane every time: MMAs of one thread execute in order
+        while (__any_sync(0xffffffffu, my_tiles > 0)) {
+            uint32_t mask = __ballot_sync(0xffffffffu, my_tiles > 0 && mbar_test(my_bar, my_parity));
+            if (mask == 0) {
+                if ((++idle & 63u) == 0) {
+                    if (*abort_now) break;
+                    const unsigned long long now = global_ns();
+                    if (deadline == 0) deadline = now + kPipeWaitNs;
+                    else if (now > deadline) {
+                        *abort_now = 1;
+                        g_tc_status = 1;
+                        break;
+                    }
+                }
+                continue;
+            }
+            idle = 0;
+            deadline = 0;
+            const bool mine = (mask >> lane) & 1u;
+            tc_fence_after();
+            while (mask) {
+                const int i = __ffs(mask) - 1;
+                mask &= mask - 1;
+                const int j = __shfl_sync(0xffffffffu, my_step, i);
+                const uint4 w = *reinterpret_cast<const uint4 *>(&steps[j].wa_off);
+                const uint32_t tile0 = smem_base + static_cast<uint32_t>(i) * slot_bytes;
+                issue_gemm(leader, tmem + w.w, tile0 + w.x, 2048, tile0 + w.y, 2048, kTileRows / 16, w.z, (dw_started >> (j - d)) & 1u);
+                dw_started |= 1u << (j - d);
+                if (leader) mma_commit(smem_addr(&bars.wdone[i]));
+            }
+            __syncwarp();
+            if (mine) {
+                my_parity ^= 1u;
+                if (++my_step == n_steps) {
+                    my_step = d;
+                    --my_tiles;
+                }
+            }
+        }
+    } else {
+        // ================= slots: loads, own MMAs, epilogues =================
+        const int slot = warp >> 2, wq = warp & 3;
+        const int row = threadIdx.x - slot * 128;
+        const uint32_t acc = tmem + slot * kAccCols;
+        const uint32_t taddr = acc + (static_cast<uint32_t>(32 * wq) << 16);
+        const uint32_t acc_bar = smem_addr(&bars.acc[slot]), ready_bar = smem_addr(&bars.ready[slot]), wdone_bar = smem_addr(&bars.wdone[slot]);
+        const uint32_t tile0 = smem_base + static_cast<uint32_t>(slot) * slot_bytes;
+        auto act_addr = [&](int l) { return tile0 + static_cast<uint32_t>(l) * kTileBytes; };
+        const uint32_t row_off = row * 128, row_swizzle = (row & 7) << 4;
+        const int chunks_x = s.ki / 8, chunks_g = s.no / 8;
+        uint32_t acc_phase = 0, wdone_phase = 0;
+        const bool leader = wq == 0 && elect_one();
+        // operands written -> the slot's warp 0 issues the step's own MMAs (and hands the wgrad to the wgrad warp)
+        auto start_step = [&](int j) {
+            fence_async_smem();
+            tc_fence_before();
+            slot_barrier(slot);
+            if (wq == 0 && !*abort_now) {
+                tc_fence_after();
+                if (j >= d && leader) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ready_bar) : "memory");
+                const uint4 own = *reinterpret_cast<const uint4 *>(&steps[j].a_off);
+                if (own.z != 0) {
+                    issue_gemm(leader, acc, tile0 + own.x, 32, own.y, (own.w & 256u) ? 2048 : 32, static_cast<int>(own.w & 255u), own.z, false);
+                    if (leader) mma_commit(acc_bar);
+                }
+                __syncwarp();
+            }
+        };
+        auto finish_step = [&](bool own, bool wgrad) {
+            if (wq == 0) {
+                if (own) pipe_wait(acc_bar, acc_phase, &abort_flag);
+                if (wgrad) pipe_wait(wdone_bar, wdone_phase, &abort_flag);
+                tc_fence_after();
+                tc_fence_before();
+            }
+            if (own) acc_phase ^= 1u;
+            if (wgrad) wdone_phase ^= 1u;
+            slot_barrier(slot);
+            tc_fence_after();
+            return !*abort_now;
+        };
+        for (long long k = slot; k < n_mine; k += S) {
+            const long long row0 = (first_tile + k * tile_stride) * kTileRows;
+            if (!*abort_now) {
+                for (int id = row; id < kTileRows * chunks_x; id += 128) {
+                    const int r = id / chunks_x, c = id - r * chunks_x;
+                    const long long grow = row0 + r;
+                    const bool inside = grow < n_rows && 8 * c < s.d_in;
+                    const T *src = inside ? x + grow * x_stride + 8 * c : x;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(tile0 + r * 128 + ((c ^ (r & 7)) << 4)), "l"(src), "r"(inside ? 16 : 0) : "memory");
+                }
+                const uint32_t go_tile = packed ? tile0 : act_addr(d + 1);
+                for (int id = row; id < kTileRows * chunks_g; id += 128) {
+                    const int r = id / chunks_g, c = id - r * chunks_g;
+                    const long long grow = row0 + r;
+                    const bool inside = grow < n_rows && 8 * c < s.d_out;
+                    const T *src = inside ? go + grow * go_stride + 8 * c : go;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(go_tile + r * 128 + (((go_chunk0 + c) ^ (r & 7)) << 4)), "l"(src), "r"(inside ? 16 : 0) : "memory");
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                async_tile_wait();
+            }
+            for (int l = 0; l < d; ++l) {  // recomputed activation of layer l -> input tile of layer l + 1
+                start_step(l);
+                if (finish_step(true, false)) {
+                    const uint32_t dst = act_addr(l + 1) + row_off;
+                    drain_row<T, ACT, false>(taddr, s.h, nullptr, [&](int chunk, uint4 packed_v) { st_shared_16(dst + ((chunk << 4) ^ row_swizzle), packed_v); });
+                }
+            }
+            for (int l = d; l >= 0; --l) {
+                const int in_pad = l == 0 ? s.ki : s.h;
+                const bool own = l > 0 || gx != nullptr;
+                start_step(2 * d - l);
+                const bool ok = finish_step(own, true);
+                if (l > 0) {
+                    if (ok) {  // dz of the layer below = dy * act'(its parked output), in place over that output
+                        const uint32_t parked = act_addr(l) + row_off;
+                        drain_row<T, TH_ACT_NONE, false>(taddr, in_pad, nullptr, [&](int chunk, uint4 gq) {
+                            const uint32_t off = (chunk << 4) ^ row_swizzle;
+                            if constexpr (ACT == TH_ACT_RELU) {
+                                const uint4 a = ld_shared_16(parked + off);
+                                gq.x = keep_where_positive<T>(gq.x, a.x);
+                                gq.y = keep_where_positive<T>(gq.y, a.y);
+                                gq.z = keep_where_positive<T>(gq.z, a.z);
+                                gq.w = keep_where_positive<T>(gq.w, a.w);
+                            }
+                            st_shared_16(parked + off, gq);
+                        });
+                    }
+                } else if (ok && gx != nullptr) {
+                    const bool live = row0 + row < n_rows;
+                    T *row_ptr = gx + (live ? row0 + row : 0) * gx_stride;
+                    drain_row<T, TH_ACT_NONE, false>(taddr, in_pad, nullptr, [&](int chunk, uint4 packed_v) {
+                        if (live && 8 * chunk < in_pad) store_chunk_to_global<T>(row_ptr, chunk, s.d_in, packed_v, gx_vec);
+                    });
+                    tc_fence_before();
+                }
+            }
+        }
+    }
+
+    // ---- flush the weight gradients (slot 0's threads; M = 64 layout: lanes 0..15 of warp w hold rows 16 w ..) ----
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (!abort_flag && n_mine > 0 && threadIdx.x < 128) {
+        const MlpGradWorkspace W = grad_workspace_layout(s, workspace);
+        const int wq = warp & 3;
+        const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
+        for (int l = 0; l <= d; ++l) {
+            const int in_pad = l == 0 ? s.ki : s.h;
+            const int in_dim = l == 0 ? s.d_in : s.d_hid, out_dim = l == d ? s.d_out : s.d_hid;
+            float *dst = W.base + (l == 0 ? W.w_in : (l == d ? W.w_out : W.w_hid + (l - 1) * s.d_hid * s.d_hid));
+            const int o = 16 * wq + lane - ((l == d && packed) ? 32 : 0);  // output row this lane holds
+            for (int first = 0; first < in_pad; first += 16) {
+                uint32_t raw[32];
+                tmem_ld16(tmem + lane_base + dw_col(l) + first, raw);
+                tmem_ld_wait();
+                if (lane < 16 && o >= 0 && o < out_dim) {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c)
+                        if (first + c < in_dim) atomicAdd(dst + o * in_dim + first + c, __uint_as_float(raw[c]));
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (is_wgrad_warp)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(static_cast<uint32_t>(tmem_cols)) : "memory");
 }
 
 bool pipe_disabled() {
@@ -980,12 +1326,57 @@ int launch_bwd_pipe(const MlpShape &s, const MlpParams &p, const void *x, int64_
     return launch_status("mlp_bwd_pipe_kernel launch");
 }
 
+bool slots_disabled() {
+    static const bool off = [] {
+        const char *v = getenv("TH_MLP_NO_SLOTS");
+        return v && v[0] == '1';
+    }();
+    return off;
+}
+
+// Slots that fit one SM: shared memory for their tiles next to the weights, tensor memory for their
+// accumulators next to the shared weight-gradient columns.
+template <typename T, int ACT, int S>
+int launch_bwd_slots_n(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, const void *go, int64_t go_stride,
+                       void *gx, int64_t gx_stride, float *workspace, int64_t rows, cudaStream_t stream) {
+    const BwdSlotPlan B = bwd_slot_plan(s, S);
+    int smem = B.total + 1024;
+    if (smem + 1024 > kSmemBudget || B.tmem_cols > 512 || 2 * s.depth + 1 > kMaxSlotSteps) return kTcNotApplicable;
+    if (smem < kSmemBudget / 2 + 1024) smem = kSmemBudget / 2 + 1024;  // one CTA per SM
+    WeightMaps maps;
+    if (!make_weight_maps(maps, s, p)) return kTcNotApplicable;
+    auto kernel = mlp_bwd_slots_kernel<T, ACT, S>;
+    if (int rc = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+                             "cudaFuncSetAttribute(mlp_bwd_slots_kernel)")) return rc;
+    const long long tiles = (rows + kTileRows - 1) / kTileRows;
+    const long long want = (tiles + S - 1) / S;
+    const long long cap = sm_count();
+    kernel<<<static_cast<unsigned>(want < cap ? want : cap), 128 * S + 32, smem, stream>>>(
+        s, p, maps, B.packed, static_cast<const T *>(x), x_stride, static_cast<const T *>(go), go_stride, static_cast<T *>(gx), gx_stride,
+        workspace, rows, gx ? rows_vector_ok(gx, gx_stride, s.d_in) : 0);
+    return launch_status("mlp_bwd_slots_kernel launch");
+}
+
+template <typename T, int ACT>
+int launch_bwd_slots(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, const void *go, int64_t go_stride,
+                     void *gx, int64_t gx_stride, float *workspace, int64_t rows, cudaStream_t stream) {
+    if (pipe_disabled() || slots_disabled()) return kTcNotApplicable;
+    // rows must move as whole 16-byte chunks (cp.async)
+    if (!rows_vector_ok(x, x_stride, s.d_in) || !rows_vector_ok(go, go_stride, s.d_out)) return kTcNotApplicable;
+    int rc = launch_bwd_slots_n<T, ACT, 4>(s, p, x, x_stride, go, go_stride, gx, gx_stride, workspace, rows, stream);
+    if (rc == kTcNotApplicable) rc = launch_bwd_slots_n<T, ACT, 3>(s, p, x, x_stride, go, go_stride, gx, gx_stride, workspace, rows, stream);
+    if (rc == kTcNotApplicable) rc = launch_bwd_slots_n<T, ACT, 2>(s, p, x, x_stride, go, go_stride, gx, gx_stride, workspace, rows, stream);
+    return rc;
+}
+
 template <typename T, int ACT, bool BIAS>
 int launch_bwd_t(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, const void *go, int64_t go_stride,
                  void *gx, int64_t gx_stride, float *workspace, int64_t rows, cudaStream_t stream) {
     // the issuer-warp kernel is built for bias-free networks whose activation derivative needs no pre-activation
     if constexpr (!BIAS && (ACT == TH_ACT_RELU || ACT == TH_ACT_NONE)) {
-        const int rc = launch_bwd_pipe<T, ACT>(s, p, x, x_stride, go, go_stride, gx, gx_stride, workspace, rows, stream);
+        int rc = launch_bwd_slots<T, ACT>(s, p, x, x_stride, go, go_stride, gx, gx_stride, workspace, rows, stream);
+        if (rc != kTcNotApplicable) return rc;
+        rc = launch_bwd_pipe<T, ACT>(s, p, x, x_stride, go, go_stride, gx, gx_stride, workspace, rows, stream);
         if (rc != kTcNotApplicable) return rc;
     }
     const TcPlan P = tc_plan(s, true);
