@@ -18,9 +18,10 @@
 // Weights (4 matrices per block) stream block by block through a two-stage cp.async ring in the
 // operand-tile layout; the same tile is read K-major by the forward GEMMs and MN-major by dgrad.
 // Weight gradients of a (tile, block, branch) leave TMEM straight into the CTA's private fp32
-// accumulator in global memory (vector red.global.add, one owner per copy, L2 resident); a
-// reduction kernel sums the copies.  The backward pass needs all 512 TMEM columns, so one CTA
-// per SM; the forward pass needs 192 (256 allocated), two CTAs per SM.
+// accumulator in global memory (vector red.global.add, one owner per copy, L2 resident), carried
+// out by four extra warps while the other eight are already in the next branch; a reduction
+// kernel sums the copies.  The backward pass needs all 512 TMEM columns, so one CTA per SM; the
+// forward pass needs 192 (256 allocated), two CTAs per SM.
 //
 // Covered here: float16 / bfloat16, 16-byte-aligned rows; backward: ReLU or no activation, no
 // biases.  Everything else stays on the mma.sync kernels.
@@ -42,7 +43,7 @@ constexpr int kFwdHid = 128;                     // forward: hidden pre-activati
 constexpr int kD1 = 128, kD2 = 192, kZ = 256, kDH = 320, kDW1 = 384, kDW2 = 448;  // backward
 
 struct RevTcPlan {
-    int tiles;     // operand tiles before the weight ring (2 forward, 4 backward)
+    int tiles;     // operand tiles before the weight ring (2 forward, 6 backward)
     int ring;      // byte offset of the ring (2 stages)
     int bias;      // fp32 [2 stages][4][64]
     int total;
@@ -51,7 +52,7 @@ struct RevTcPlan {
 
 __host__ __device__ inline RevTcPlan rev_tc_plan(bool backward) {
     RevTcPlan p{};
-    p.tiles = backward ? 4 : 2;
+    p.tiles = backward ? 6 : 2;
     p.ring = p.tiles * kTileBytes;
     p.bias = p.ring + 2 * kStageBytes;
     p.total = p.bias + 2 * 4 * kMaxDim * 4;
@@ -290,26 +291,71 @@ rev_fwd_tc_kernel(const RevShape s, const RevParams p, const __grid_constant__ R
 // instead of 16 half-used ones), which is what the L2's reduction rate is counted in.
 __host__ __device__ inline int dw_private_index(int row, int col) { return ((col >> 2) * 64 + row) * 4 + (col & 3); }
 
-__device__ __forceinline__ void flush_dw_private(uint32_t taddr, const Seat &seat, int out_dim, int in_dim, float *dst) {
-    const int n = in_dim / kGroups, first = seat.group * (n / 8);  // this thread's columns / first 8-column piece
+// The backward kernel runs 256 "main" threads (the chain: issue, wait, epilogue) and 128 "flush" threads
+// that carry the weight gradients of a pass out of TMEM while the main threads are already in the next pass.
+constexpr int kRevFlushThreads = 128;
+
+// CTA barrier of the main threads only
+__device__ __forceinline__ void main_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+__device__ __forceinline__ void main_publish() {
+    fence_async_smem();
+    tc_fence_before();
+    main_sync();
+}
+
+// Bounded wait that also gives up when somebody else has: false = do not go on.
+__device__ __forceinline__ bool rev_wait(uint32_t bar, uint32_t parity, int *abort_flag) {
+    for (int poll = 0; poll < kWaitPolls; ++poll) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if ((poll & 63) == 63 && *reinterpret_cast<volatile int *>(abort_flag)) return false;
+    }
+    *reinterpret_cast<volatile int *>(abort_flag) = 1;
+    return false;
+}
+
+// cta_wait_mma for the main threads: warp 0 polls, the others park at the main barrier
+__device__ __forceinline__ bool main_wait_mma(uint32_t mbar, uint32_t &phase, int *abort_flag) {
+    if (threadIdx.x < 32) {
+        rev_wait(mbar, phase, abort_flag);
+        tc_fence_after();
+        tc_fence_before();
+    }
+    phase ^= 1;
+    main_sync();
+    tc_fence_after();
+    return *reinterpret_cast<volatile int *>(abort_flag) == 0;
+}
+
+// One flush warp's share (TMEM lanes 32 q .. 32 q + 15 = gradient rows 16 q .. 16 q + 15) of one accumulator
+__device__ __forceinline__ void flush_dw_quadrant(uint32_t tmem, int q, uint32_t col, int out_dim, int in_dim, float *dst) {
     const int lane = threadIdx.x & 31;
-    const int m = 16 * ((threadIdx.x >> 5) & 3) + lane;
+    const int m = 16 * q + lane;
     const bool owner = lane < 16 && m < out_dim;
-    // fire-and-forget vector reductions: no round trip to wait for, and nobody else touches this copy
-    for_each_piece(taddr + seat.group * n, n, [&](int u, const uint32_t(&piece)[8]) {
+    const uint32_t taddr = tmem + (static_cast<uint32_t>(32 * q) << 16) + col;
+    for (int first = 0; first < in_dim; first += 16) {
+        uint32_t raw[32];
+        tmem_ld16(taddr + first, raw);
+        tmem_ld_wait();
         if (owner) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
-                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + dw_private_index(m, 8 * (first + u) + 4 * h)),
-                             "f"(__uint_as_float(piece[4 * h])), "f"(__uint_as_float(piece[4 * h + 1])),
-                             "f"(__uint_as_float(piece[4 * h + 2])), "f"(__uint_as_float(piece[4 * h + 3]))
+            for (int h = 0; h < 4; ++h)
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + dw_private_index(m, first + 4 * h)),
+                             "f"(__uint_as_float(raw[4 * h])), "f"(__uint_as_float(raw[4 * h + 1])),
+                             "f"(__uint_as_float(raw[4 * h + 2])), "f"(__uint_as_float(raw[4 * h + 3]))
                              : "memory");
         }
-    });
+    }
 }
 
 template <typename T, int ACT>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(kTcThreads + kRevFlushThreads, 1)
 rev_bwd_tc_kernel(const RevShape s, const RevParams p, const __grid_constant__ RevWeightMaps maps, const int use_tma,
                   const T *__restrict__ y, long long y_stride,
                   const T *__restrict__ go, long long go_stride, T *__restrict__ gx, long long gx_stride,
@@ -321,153 +367,189 @@ rev_bwd_tc_kernel(const RevShape s, const RevParams p, const __grid_constant__ R
     __shared__ int abort_flag;
     const RevTcPlan P = rev_tc_plan(true);
     constexpr int bf16 = std::is_same<T, __half>::value ? 0 : 1;
-    unsigned char *u_tile = smem, *h_tile = smem + kTileBytes, *dy_tile = smem + 2 * kTileBytes, *dz_tile = smem + 3 * kTileBytes;
+    // U (the branch's input, 16-bit) and DY (the gradient of its output) alternate between two tiles each: the
+    // epilogue of a pass writes the next pass's copies while this pass's weight-gradient MMAs still read theirs
+    unsigned char *u_tiles = smem, *h_tile = smem + 2 * kTileBytes, *dy_tiles = smem + 3 * kTileBytes, *dz_tile = smem + 5 * kTileBytes;
+    const bool is_flush = threadIdx.x >= kTcThreads;
 
     __shared__ __align__(8) unsigned long long ring_bars[2];
+    // wgrad_bar: the weight-gradient MMAs of a pass are done (one commit per pass); flushed_bar: the flush warps
+    // have read them out (one arrival per flush warp), so the next pass may overwrite the accumulators
+    __shared__ __align__(8) unsigned long long wgrad_bar, flushed_bar;
     if (threadIdx.x == 0) {
         abort_flag = 0;
         asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&ring_bars[0])), "r"(1u) : "memory");
         asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&ring_bars[1])), "r"(1u) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&wgrad_bar)), "r"(1u) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&flushed_bar)), "r"(static_cast<uint32_t>(kRevFlushThreads / 32)) : "memory");
     }
-    for (int e = threadIdx.x; e < 4 * kTileBytes / 16; e += kTcThreads) reinterpret_cast<uint4 *>(smem)[e] = make_uint4(0, 0, 0, 0);
+    for (int e = threadIdx.x; e < P.tiles * kTileBytes / 16; e += blockDim.x) reinterpret_cast<uint4 *>(smem)[e] = make_uint4(0, 0, 0, 0);
     const long long n_tiles = (n_rows + kTileRows - 1) / kTileRows;
-    if (!use_tma && static_cast<long long>(blockIdx.x) < n_tiles) prefetch_weights<T>(smem, P, s, p, s.blocks - 1, 0);
+    if (!is_flush && !use_tma && static_cast<long long>(blockIdx.x) < n_tiles) prefetch_weights<T>(smem, P, s, p, s.blocks - 1, 0);
     const uint32_t tmem = cta_setup(&tmem_holder, &mbar, P.tmem_cols);  // publishes the barrier inits
-    if (use_tma && static_cast<long long>(blockIdx.x) < n_tiles) {
-        prefetch_weights_tma<T>(smem, P, s, p, maps, ring_bars, s.blocks - 1, 0);
-        ring_wait(ring_bars, 0, &abort_flag);
-    }
-    const uint32_t bar = smem_addr(&mbar);
-    const Seat seat;
-    const uint32_t taddr = tmem + seat.lane_base;
-    uint32_t phase = 0;
-    int step = 0;
-    // Weight gradients of a pass stay in TMEM until the NEXT pass has issued its first GEMMs: the flush
-    // (tcgen05.ld + vector reductions, ~1 200 cycles) then runs under those GEMMs instead of before them.
-    float *pending_dw1 = nullptr, *pending_dw2 = nullptr;
-    auto flush_pending = [&]() {
-        if (pending_dw1) {
-            flush_dw_private(taddr + kDW1, seat, s.hid, s.half, pending_dw1);
-            flush_dw_private(taddr + kDW2, seat, s.half, s.hid, pending_dw2);
-            pending_dw1 = pending_dw2 = nullptr;
-        }
-    };
     float *cta_acc = workspace + static_cast<size_t>(blockIdx.x) * rev_cta_floats(s);
-    // instruction descriptors: forward-type, dgrad (B MN-major), reconstruction (A negated), wgrad (both MN-major, M = 64)
-    const uint32_t id_z = instr_desc(128, s.hid, bf16, 0, 0);
-    const uint32_t id_dh = instr_desc(128, s.hid, bf16, 0, 1);
-    const uint32_t id_undo = instr_desc(128, s.half, bf16, 0, 0) | (1u << 13);
-    const uint32_t id_din = instr_desc(128, s.half, bf16, 0, 1);
-    const uint32_t id_dw2 = instr_desc(64, s.hid, bf16, 1, 1), id_dw1 = instr_desc(64, s.half, bf16, 1, 1);
+    const uint32_t wgrad_addr = smem_addr(&wgrad_bar), flushed_addr = smem_addr(&flushed_bar);
 
-    for (long long tile = blockIdx.x; tile < n_tiles && !abort_flag; tile += gridDim.x) {
-        const long long row0 = tile * kTileRows;
-        const bool live = row0 + seat.row < n_rows;
-        // y1 -> U (input of the last G), y2 -> scratch, go1 -> scratch, go2 -> DY (gradient of G's output)
-        async_tile_load<T>(u_tile, y, y_stride, row0, n_rows, s.half, s.half);
-        async_tile_load<T>(h_tile, y + s.half, y_stride, row0, n_rows, s.half, s.half);
-        async_tile_load<T>(dz_tile, go, go_stride, row0, n_rows, s.half, s.half);
-        async_tile_load<T>(dy_tile, go + s.half, go_stride, row0, n_rows, s.half, s.half);
-        async_tile_wait();
-        __syncthreads();
-        tile_row_to_tmem<T>(u_tile, seat, s.half, taddr + kS1);
-        tile_row_to_tmem<T>(h_tile, seat, s.half, taddr + kS2);
-        tile_row_to_tmem<T>(dz_tile, seat, s.half, taddr + kD1);
-        tile_row_to_tmem<T>(dy_tile, seat, s.half, taddr + kD2);
-        tmem_st_wait();
-        publish_tiles();
-
-        for (int k = s.blocks - 1; k >= 0 && !abort_flag; --k, ++step) {
-            const int stage = step & 1;
-            const bool more = k > 0 || tile + gridDim.x < n_tiles;
-            if (more) {
-                if (use_tma) prefetch_weights_tma<T>(smem, P, s, p, maps, ring_bars, k > 0 ? k - 1 : s.blocks - 1, stage ^ 1);
-                else prefetch_weights<T>(smem, P, s, p, k > 0 ? k - 1 : s.blocks - 1, stage ^ 1);
-            }
-            const unsigned char *w = smem + P.ring + stage * kStageBytes;
-            float *block_acc = cta_acc + static_cast<size_t>(k) * 4 * kMatFloats;
-#pragma unroll 1
-            for (int pass = 0; pass < 2; ++pass) {
-                // pass 0 undoes y2 = x2 + G(y1): input stream S1, output stream S2, gradient flows D2 -> D1
-                // pass 1 undoes y1 = x1 + F(x2): input stream S2, output stream S1, gradient flows D1 -> D2
-                const int m1 = pass == 0 ? 2 : 0, m2 = m1 + 1;
-                const uint32_t w1 = smem_addr(w + m1 * kWTileBytes), w2 = smem_addr(w + m2 * kWTileBytes);
-                const uint32_t out_col = pass == 0 ? kS2 : kS1, in_d_col = pass == 0 ? kD1 : kD2;
-                bool leader = false;
-                // step A: z = U . W1^T and dh = DY . W2 together
-                if (threadIdx.x < 32) {
-                    leader = elect_one();
+    if (is_flush) {
+        // ================= weight gradients out of TMEM, one pass behind the main threads =================
+        const int q = (threadIdx.x >> 5) & 3;
+        uint32_t n = 0;  // passes flushed so far
+        bool alive = true;
+        for (long long tile = blockIdx.x; alive && tile < n_tiles; tile += gridDim.x) {
+            for (int k = s.blocks - 1; alive && k >= 0; --k) {
+                float *block_acc = cta_acc + static_cast<size_t>(k) * 4 * kMatFloats;
+                for (int pass = 0; pass < 2; ++pass, ++n) {
+                    alive = __all_sync(0xffffffffu, rev_wait(wgrad_addr, n & 1u, &abort_flag));
+                    if (!alive) break;
                     tc_fence_after();
-                    issue_gemm(leader, tmem + kZ, smem_addr(u_tile), 32, w1, 32, s.half / 16, id_z, false);
-                    issue_gemm(leader, tmem + kDH, smem_addr(dy_tile), 32, w2, 2048, s.half / 16, id_dh, false);
-                    if (leader) mma_commit(bar);
+                    const int m1 = pass == 0 ? 2 : 0;
+                    flush_dw_quadrant(tmem, q, kDW1, s.hid, s.half, block_acc + m1 * kMatFloats);
+                    flush_dw_quadrant(tmem, q, kDW2, s.half, s.hid, block_acc + (m1 + 1) * kMatFloats);
+                    tc_fence_before();
                     __syncwarp();
+                    if ((threadIdx.x & 31) == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(flushed_addr) : "memory");
                 }
-                flush_pending();  // the previous pass's weight gradients, while the GEMMs above run
-                cta_wait_mma(bar, phase, &abort_flag);
-                {
-                    // h = act(z) first (also the ReLU mask), then dz = dh where h > 0
-                    const int n = s.hid / kGroups, first = seat.group * (n / 8);
-                    const uint32_t row_off = seat.row * 128, row_swizzle = (seat.row & 7) << 4;
-                    const uint32_t h_row = smem_addr(h_tile) + row_off, dz_row = smem_addr(dz_tile) + row_off;
-                    for_each_piece(taddr + kZ + seat.group * n, n, [&](int u, const uint32_t(&piece)[8]) {
-                        st_shared_16(h_row + (((first + u) << 4) ^ row_swizzle), finish8<T, ACT, false>(piece, nullptr));
-                    });
-                    for_each_piece(taddr + kDH + seat.group * n, n, [&](int u, const uint32_t(&piece)[8]) {
-                        const uint32_t off = ((first + u) << 4) ^ row_swizzle;
-                        uint4 g = finish8<T, TH_ACT_NONE, false>(piece, nullptr);
-                        if constexpr (ACT == TH_ACT_RELU) {
-                            const uint4 h = ld_shared_16(h_row + off);  // this thread's own store above
-                            g.x = keep_where_positive<T>(g.x, h.x);
-                            g.y = keep_where_positive<T>(g.y, h.y);
-                            g.z = keep_where_positive<T>(g.z, h.z);
-                            g.w = keep_where_positive<T>(g.w, h.w);
-                        }
-                        st_shared_16(dz_row + off, g);
-                    });
-                }
-                publish_tiles();
-                // step B: undo the branch, push the gradient through, form both weight gradients
-                if (threadIdx.x < 32) {
-                    leader = elect_one();
-                    tc_fence_after();
-                    issue_gemm(leader, tmem + out_col, smem_addr(h_tile), 32, w2, 32, s.hid / 16, id_undo, true);
-                    issue_gemm(leader, tmem + in_d_col, smem_addr(dz_tile), 32, w1, 2048, s.hid / 16, id_din, true);
-                    issue_gemm(leader, tmem + kDW2, smem_addr(dy_tile), 2048, smem_addr(h_tile), 2048, kTileRows / 16, id_dw2, false);
-                    issue_gemm(leader, tmem + kDW1, smem_addr(dz_tile), 2048, smem_addr(u_tile), 2048, kTileRows / 16, id_dw1, false);
-                }
-                commit_and_wait(leader, bar, phase, &abort_flag);
-                // next pass: its input is the stream just reconstructed, its output gradient the one just updated
-                stream_epilogue<T, false>(taddr + out_col, seat, s.half, nullptr, u_tile, nullptr, false);
-                stream_epilogue<T, false>(taddr + in_d_col, seat, s.half, nullptr, dy_tile, nullptr, false);
-                pending_dw1 = block_acc + m1 * kMatFloats;
-                pending_dw2 = block_acc + m2 * kMatFloats;
-                if (pass == 1) {  // next block's weights have landed
-                    if (!use_tma) async_tile_wait();
-                    else if (more) ring_wait(ring_bars, step + 1, &abort_flag);
-                }
-                publish_tiles();
             }
         }
-        // the stream is now the reconstructed input, the gradient stream the input gradient
-        if (!abort_flag) {
+    } else {
+        // ================= the chain =================
+        if (use_tma && static_cast<long long>(blockIdx.x) < n_tiles) {
+            prefetch_weights_tma<T>(smem, P, s, p, maps, ring_bars, s.blocks - 1, 0);
+            ring_wait(ring_bars, 0, &abort_flag);
+        }
+        const uint32_t bar = smem_addr(&mbar);
+        const Seat seat;
+        const uint32_t taddr = tmem + seat.lane_base;
+        uint32_t phase = 0;
+        int step = 0;
+        uint32_t n = 0;  // passes started so far; pass n reads U / DY copy n & 1 and writes copy (n + 1) & 1
+        // instruction descriptors: forward-type, dgrad (B MN-major), reconstruction (A negated), wgrad (both MN-major, M = 64)
+        const uint32_t id_z = instr_desc(128, s.hid, bf16, 0, 0);
+        const uint32_t id_dh = instr_desc(128, s.hid, bf16, 0, 1);
+        const uint32_t id_undo = instr_desc(128, s.half, bf16, 0, 0) | (1u << 13);
+        const uint32_t id_din = instr_desc(128, s.half, bf16, 0, 1);
+        const uint32_t id_dw2 = instr_desc(64, s.hid, bf16, 1, 1), id_dw1 = instr_desc(64, s.half, bf16, 1, 1);
+        volatile int *abort_now = &abort_flag;
+
+        for (long long tile = blockIdx.x; tile < n_tiles && !*abort_now; tile += gridDim.x) {
+            const long long row0 = tile * kTileRows;
+            const bool live = row0 + seat.row < n_rows;
+            unsigned char *u_in = u_tiles + (n & 1u) * kTileBytes, *dy_in = dy_tiles + (n & 1u) * kTileBytes;
+            // the scratch tiles below were operands of the previous tile's last weight-gradient MMAs
+            if (n > 0) {
+                if (threadIdx.x < 32) rev_wait(wgrad_addr, (n - 1) & 1u, &abort_flag);
+                main_sync();
+            }
+            // y1 -> U (input of the last G), y2 -> scratch, go1 -> scratch, go2 -> DY (gradient of G's output)
+            async_tile_load<T>(u_in, y, y_stride, row0, n_rows, s.half, s.half);
+            async_tile_load<T>(h_tile, y + s.half, y_stride, row0, n_rows, s.half, s.half);
+            async_tile_load<T>(dz_tile, go, go_stride, row0, n_rows, s.half, s.half);
+            async_tile_load<T>(dy_in, go + s.half, go_stride, row0, n_rows, s.half, s.half);
+            async_tile_wait();
+            main_sync();
+            tile_row_to_tmem<T>(u_in, seat, s.half, taddr + kS1);
+            tile_row_to_tmem<T>(h_tile, seat, s.half, taddr + kS2);
+            tile_row_to_tmem<T>(dz_tile, seat, s.half, taddr + kD1);
+            tile_row_to_tmem<T>(dy_in, seat, s.half, taddr + kD2);
+            tmem_st_wait();
+            main_publish();
+
+            for (int k = s.blocks - 1; k >= 0 && !*abort_now; --k, ++step) {
+                const int stage = step & 1;
+                const bool more = k > 0 || tile + gridDim.x < n_tiles;
+                if (more) {
+                    if (use_tma) prefetch_weights_tma<T>(smem, P, s, p, maps, ring_bars, k > 0 ? k - 1 : s.blocks - 1, stage ^ 1);
+                    else prefetch_weights<T>(smem, P, s, p, k > 0 ? k - 1 : s.blocks - 1, stage ^ 1);
+                }
+                const unsigned char *w = smem + P.ring + stage * kStageBytes;
 #pragma unroll 1
-            for (int q = 0; q < 4; ++q) {
-                // q: 0 = dx1 (D1), 1 = dx2 (D2), 2 = x1 (S1), 3 = x2 (S2)
-                T *base = q < 2 ? gx : x_rec;
-                const long long stride = q < 2 ? gx_stride : xr_stride;
-                const uint32_t col = q == 0 ? kD1 : (q == 1 ? kD2 : (q == 2 ? kS1 : kS2));
-                if (base != nullptr)
-                    stream_epilogue<T, false>(taddr + col, seat, s.half, nullptr, nullptr,
-                                              base + (live ? row0 + seat.row : 0) * stride + (q & 1) * s.half, live);
+                for (int pass = 0; pass < 2; ++pass, ++n) {
+                    // pass 0 undoes y2 = x2 + G(y1): input stream S1, output stream S2, gradient flows D2 -> D1
+                    // pass 1 undoes y1 = x1 + F(x2): input stream S2, output stream S1, gradient flows D1 -> D2
+                    const int m1 = pass == 0 ? 2 : 0, m2 = m1 + 1;
+                    const uint32_t w1 = smem_addr(w + m1 * kWTileBytes), w2 = smem_addr(w + m2 * kWTileBytes);
+                    const uint32_t out_col = pass == 0 ? kS2 : kS1, in_d_col = pass == 0 ? kD1 : kD2;
+                    const uint32_t u_cur = smem_addr(u_tiles + (n & 1u) * kTileBytes), dy_cur = smem_addr(dy_tiles + (n & 1u) * kTileBytes);
+                    unsigned char *u_next = u_tiles + ((n + 1) & 1u) * kTileBytes, *dy_next = dy_tiles + ((n + 1) & 1u) * kTileBytes;
+                    // step A: z = U . W1^T and dh = DY . W2 together.  This commit also covers the previous pass's
+                    // weight-gradient MMAs (a commit tracks everything its thread issued before), which read the
+                    // h and dz tiles the epilogue below overwrites.
+                    if (threadIdx.x < 32) {
+                        const bool leader = elect_one();
+                        tc_fence_after();
+                        issue_gemm(leader, tmem + kZ, u_cur, 32, w1, 32, s.half / 16, id_z, false);
+                        issue_gemm(leader, tmem + kDH, dy_cur, 32, w2, 2048, s.half / 16, id_dh, false);
+                        if (leader) mma_commit(bar);
+                        __syncwarp();
+                    }
+                    main_wait_mma(bar, phase, &abort_flag);
+                    {
+                        // h = act(z) first (also the ReLU mask), then dz = dh where h > 0
+                        const int nn = s.hid / kGroups, first = seat.group * (nn / 8);
+                        const uint32_t row_off = seat.row * 128, row_swizzle = (seat.row & 7) << 4;
+                        const uint32_t h_row = smem_addr(h_tile) + row_off, dz_row = smem_addr(dz_tile) + row_off;
+                        for_each_piece(taddr + kZ + seat.group * nn, nn, [&](int u, const uint32_t(&piece)[8]) {
+                            st_shared_16(h_row + (((first + u) << 4) ^ row_swizzle), finish8<T, ACT, false>(piece, nullptr));
+                        });
+                        for_each_piece(taddr + kDH + seat.group * nn, nn, [&](int u, const uint32_t(&piece)[8]) {
+                            const uint32_t off = ((first + u) << 4) ^ row_swizzle;
+                            uint4 g = finish8<T, TH_ACT_NONE, false>(piece, nullptr);
+                            if constexpr (ACT == TH_ACT_RELU) {
+                                const uint4 h = ld_shared_16(h_row + off);  // this thread's own store above
+                                g.x = keep_where_positive<T>(g.x, h.x);
+                                g.y = keep_where_positive<T>(g.y, h.y);
+                                g.z = keep_where_positive<T>(g.z, h.z);
+                                g.w = keep_where_positive<T>(g.w, h.w);
+                            }
+                            st_shared_16(dz_row + off, g);
+                        });
+                    }
+                    main_publish();
+                    // step B: undo the branch and push the gradient through (waited for below); then both weight
+                    // gradients, committed on their own for the flush warps
+                    if (threadIdx.x < 32) {
+                        const bool leader = elect_one();
+                        tc_fence_after();
+                        issue_gemm(leader, tmem + out_col, smem_addr(h_tile), 32, w2, 32, s.hid / 16, id_undo, true);
+                        issue_gemm(leader, tmem + in_d_col, smem_addr(dz_tile), 32, w1, 2048, s.hid / 16, id_din, true);
+                        if (leader) mma_commit(bar);
+                        // the accumulators still hold the previous pass's sums until the flush warps have read them
+                        const bool free_dw = n == 0 || __all_sync(0xffffffffu, rev_wait(flushed_addr, (n - 1) & 1u, &abort_flag));
+                        if (free_dw) {
+                            tc_fence_after();
+                            issue_gemm(leader, tmem + kDW2, dy_cur, 2048, smem_addr(h_tile), 2048, kTileRows / 16, id_dw2, false);
+                            issue_gemm(leader, tmem + kDW1, smem_addr(dz_tile), 2048, u_cur, 2048, kTileRows / 16, id_dw1, false);
+                            if (leader) mma_commit(wgrad_addr);
+                        }
+                        __syncwarp();
+                    }
+                    main_wait_mma(bar, phase, &abort_flag);
+                    // next pass: its input is the stream just reconstructed, its output gradient the one just updated
+                    stream_epilogue<T, false>(taddr + out_col, seat, s.half, nullptr, u_next, nullptr, false);
+                    stream_epilogue<T, false>(taddr + in_d_col, seat, s.half, nullptr, dy_next, nullptr, false);
+                    if (pass == 1) {  // next block's weights have landed
+                        if (!use_tma) async_tile_wait();
+                        else if (more) ring_wait(ring_bars, step + 1, &abort_flag);
+                    }
+                    main_publish();
+                }
             }
-            tc_fence_before();
-            __syncthreads();
+            // the stream is now the reconstructed input, the gradient stream the input gradient
+            if (!*abort_now) {
+#pragma unroll 1
+                for (int q = 0; q < 4; ++q) {
+                    // q: 0 = dx1 (D1), 1 = dx2 (D2), 2 = x1 (S1), 3 = x2 (S2)
+                    T *base = q < 2 ? gx : x_rec;
+                    const long long stride = q < 2 ? gx_stride : xr_stride;
+                    const uint32_t col = q == 0 ? kD1 : (q == 1 ? kD2 : (q == 2 ? kS1 : kS2));
+                    if (base != nullptr)
+                        stream_epilogue<T, false>(taddr + col, seat, s.half, nullptr, nullptr,
+                                                  base + (live ? row0 + seat.row : 0) * stride + (q & 1) * s.half, live);
+                }
+                tc_fence_before();
+                main_sync();
+            }
         }
-    }
-    if (!abort_flag) {
-        tc_fence_after();
-        flush_pending();
     }
     if (abort_flag) g_tc_status = 1;
     cta_teardown(tmem, P.tmem_cols);
@@ -577,7 +659,7 @@ int launch_rev_bwd_t(const RevShape &s, const RevParams &p, const void *y, int64
                              "cudaFuncSetAttribute(rev_bwd_tc_kernel)")) return rc;
     RevWeightMaps maps;
     const int use_tma = make_rev_maps(maps, s, p);
-    kernel<<<n_ctas, kTcThreads, smem, stream>>>(s, p, maps, use_tma, static_cast<const T *>(y), y_stride,
+    kernel<<<n_ctas, kTcThreads + kRevFlushThreads, smem, stream>>>(s, p, maps, use_tma, static_cast<const T *>(y), y_stride,
                                                 static_cast<const T *>(go), go_stride, static_cast<T *>(gx), gx_stride,
                                                 static_cast<T *>(x_rec), xr_stride, workspace, rows);
     if (int rc = launch_status("rev_bwd_tc_kernel launch")) return rc;
