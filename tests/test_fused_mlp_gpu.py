@@ -171,6 +171,44 @@ def test_many_row_tiles_per_cta(dtype, depth, d_hid):
             assert nerr(gg, w) <= (tight if name == "y" else 10 * tight), f"{name}: {nerr(gg, w)}"
 
 
+@pytest.mark.parametrize("d_in,d_hid,d_out,depth", [(64, 64, 64, 2), (64, 32, 16, 3), (16, 64, 32, 1), (48, 64, 8, 2)])
+def test_many_row_tiles_when_the_output_gradient_has_its_own_tile(d_in, d_hid, d_out, depth):
+    # the backward with several row tiles per CTA packs the output gradient into the feature tile only when both are
+    # at most 32 wide; wider ones take a tile of their own (and d_in = 48 is padded to 64 columns)
+    dtype = torch.float16
+    rows = 148 * 4 * 128 * 2 + 333
+    p = make_params(d_in, d_hid, d_out, depth, dtype, bias=False, seed=d_in + depth)
+    g = torch.Generator().manual_seed(d_out)
+    x = torch.randn(1, rows, d_in, generator=g).to(dtype)
+    go = torch.randn(1, rows, d_out, generator=g).mul(1e-1).to(dtype).float()
+    want, got = run_both(x, p, go, "relu", rounded=True)
+    for name, w, gg in zip(NAMES, want, got):
+        assert (w is None) == (gg is None), name
+        if w is None:
+            continue
+        if name == "dx":
+            assert rows_outside(gg, w, 2e-3) <= 1e-2 and nerr(gg, w) <= 0.5
+        else:
+            assert nerr(gg, w) <= (2e-3 if name == "y" else 2e-2), f"{name}: {nerr(gg, w)}"
+
+
+def test_backward_without_an_input_gradient():
+    # x does not require a gradient: the input layer's dgrad GEMM is skipped, its weight gradient is not
+    dtype = torch.float16
+    rows = 148 * 4 * 128 + 5
+    p = make_params(32, 64, 16, 2, dtype, bias=False, seed=3)
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(1, rows, 32, generator=g).to(dtype)
+    go = torch.randn(1, rows, 16, generator=g).mul(1e-1).to(dtype).float()
+    want = oracle.forward_backward_storage_rounded(x, p["w_in"], None, p["w_out"], None, p["w_hid"], None, go, "relu")
+    leaves = {k: (None if v is None else v.cuda().requires_grad_(True)) for k, v in p.items()}
+    y = fully_fused_mlp(x.cuda(), leaves["w_in"], None, leaves["w_out"], None, leaves["w_hid"], None, activation="relu")
+    y.backward(go.cuda().to(dtype))
+    for name, k in (("dw_in", "w_in"), ("dw_out", "w_out"), ("dw_hid", "w_hid")):
+        w = want[NAMES.index(name)]
+        assert nerr(leaves[k].grad, w) <= 2e-2, f"{name}: {nerr(leaves[k].grad, w)}"
+
+
 @pytest.mark.parametrize("rows", [1, 127, 128, 129, 4 * 128 + 1])
 def test_row_count_edges_on_the_tensor_core_path(rows):
     # aligned 32 -> 64 -> 64 -> 16 without biases: the TMA-fed kernels, whose last tile is partly
