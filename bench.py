@@ -49,6 +49,7 @@ L2_BYTES = 126 * 1024 * 1024
 # ncu figures are not typed in here: a summary under profiles/ that wants one of its captured figures
 # quoted beside the timed number carries a line
 #   bench-record: workload=<name> entry=<C-ABI entry> dram_bytes_per_launch=<int> l2_requests_per_launch=<int>
+#                 l2_sectors_per_launch=<int> tensor_pipe_pct=<float>          (any subset of the four figures)
 # and the JSON line names the file it took them from.  No such line -> null.
 RECORD = re.compile(r"bench-record:\s*(.*)")
 
@@ -64,7 +65,7 @@ def ncu_records(workload):
             fields = dict(kv.split("=", 1) for kv in m.group(1).split() if "=" in kv)
             if fields.get("workload") == workload and "entry" in fields:
                 rec = {"source": os.path.relpath(path, ROOT)}
-                for key in ("dram_bytes_per_launch", "l2_requests_per_launch"):
+                for key in ("dram_bytes_per_launch", "l2_requests_per_launch", "l2_sectors_per_launch", "tensor_pipe_pct"):
                     if key in fields:
                         rec[key] = float(fields[key])
                 found[fields["entry"]] = rec
@@ -646,7 +647,23 @@ def main():
         achieved, peak, unit = per_launch_amount / per_launch_s / 1e9, peaks["hbm_gbs"], "GB/s"
     else:
         achieved, peak, unit = per_launch_amount / per_launch_s / 1e12, peaks["tflops"], "TFLOP/s"
-    record = ncu_records(args.workload).get(top, {})
+    records = ncu_records(args.workload)
+    record = records.get(top, {})
+    # ncu figures of every entry point that has a summary: DRAM and L2 GB/s over this run's launch time, tensor-pipe
+    # utilisation as captured
+    for entry, info in breakdown.items():
+        rec = records.get(entry)
+        if not rec:
+            continue
+        launch_s = kernels[entry][1] / kernels[entry][0] * 1e-3
+        ncu = {"source": rec["source"]}
+        if "dram_bytes_per_launch" in rec:
+            ncu["dram_gbs"] = rec["dram_bytes_per_launch"] / launch_s / 1e9
+        if "l2_sectors_per_launch" in rec:
+            ncu["l2_gbs"] = rec["l2_sectors_per_launch"] * 32 / launch_s / 1e9
+        if "tensor_pipe_pct" in rec:
+            ncu["tensor_pipe_pct"] = rec["tensor_pipe_pct"]
+        info["ncu"] = ncu
     roofline = {"kernel": top, "bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
                 "traffic": record.get("dram_bytes_per_launch"), "traffic_source": record.get("source"),
                 "peak_source": peaks["source"], "algorithmic_per_launch": per_launch_amount,
