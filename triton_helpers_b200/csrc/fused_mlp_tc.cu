@@ -157,7 +157,7 @@ mlp_fwd_tc_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ W
 // Every mbarrier wait is bounded and watches a shared abort flag; after an abort a slot keeps the
 // SAME sequence of named barriers (doing no work) so nobody is left waiting at one.
 
-constexpr int kMaxSlots = 4;
+constexpr int kMaxSlots = 5;
 
 struct SlotBarriers {
     unsigned long long in_full[kMaxSlots][2];
@@ -203,7 +203,9 @@ __device__ __forceinline__ void slot_barrier(int slot) {
 
 // One accumulator row (out_pad = 16, 32 or 64 columns) -> bias, activation, rounding -> 16-byte
 // chunks, each handed to `sink(chunk index, packed values)`; 32 columns per TMEM load.
-template <typename T, int ACT, bool BIAS, int S, bool MSE>
+// TA: hidden activations go back to the tensor core through tensor memory (32 more columns per slot) instead of
+// the operand tile in shared memory; the first layer still reads the TMA-fetched input tile.
+template <typename T, int ACT, bool BIAS, int S, bool MSE, bool TA>
 __global__ void __launch_bounds__(128 * S, 1)
 mlp_fwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__ WeightMaps maps,
                     const __grid_constant__ CUtensorMap x_map, T *__restrict__ y, long long y_stride, long long n_rows,
@@ -216,7 +218,7 @@ mlp_fwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
     __shared__ __align__(8) SlotBarriers bars;
     const TcPlan P = tc_plan(s, false, 2 * S);
     constexpr int bf16 = std::is_same<T, __half>::value ? 0 : 1;
-    constexpr uint32_t kTmemCols = S * kAccCols <= 256 ? 256 : 512;
+    constexpr uint32_t kTmemCols = S * (kAccCols + (TA ? 32 : 0)) <= 256 ? 256 : 512;
     const int warp = threadIdx.x >> 5;
 
     // ---- set-up: barriers, biases, weights, TMEM ----
@@ -272,6 +274,8 @@ mlp_fwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
     const int row = 32 * (warp & 3) + (threadIdx.x & 31);
     const uint32_t acc = tmem + slot * kAccCols;
     const uint32_t taddr = acc + (static_cast<uint32_t>(32 * (warp & 3)) << 16);
+    const uint32_t act_tmem = tmem + S * kAccCols + slot * 32;  // TA: the slot's hidden activations, 16-bit pairs
+    const uint32_t act_taddr = act_tmem + (static_cast<uint32_t>(32 * (warp & 3)) << 16);
     const uint32_t acc_bar = smem_addr(&bars.acc_full[slot]);
     unsigned char *buffers = smem + 2 * slot * kTileBytes;
     uint32_t acc_phase = 0;  // tracked by the issuer warp
@@ -309,8 +313,12 @@ mlp_fwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
                 if (__all_sync(0xffffffffu, !*reinterpret_cast<volatile int *>(&abort_flag))) {
                     const bool leader = elect_one();
                     tc_fence_after();
-                    issue_gemm(leader, acc, tile_addr, 32, smem_addr(weight_tile(smem, P, s, l)), 32, in_pad / 16,
-                               instr_desc(128, out_pad, bf16, 0, 0), false);
+                    if (TA && l > 0)
+                        issue_gemm_ta(leader, acc, act_tmem, smem_addr(weight_tile(smem, P, s, l)), 32, in_pad / 16,
+                                      instr_desc(128, out_pad, bf16, 0, 0), false);
+                    else
+                        issue_gemm(leader, acc, tile_addr, 32, smem_addr(weight_tile(smem, P, s, l)), 32, in_pad / 16,
+                                   instr_desc(128, out_pad, bf16, 0, 0), false);
                     if (leader) mma_commit(acc_bar);
                     __syncwarp();
                     pipe_wait(acc_bar, acc_phase, &abort_flag);
@@ -322,10 +330,15 @@ mlp_fwd_pipe_kernel(const MlpShape s, const MlpParams p, const __grid_constant__
                 tc_fence_after();
                 const float *layer_bias = bias + l * kMaxDim;
                 if (l < s.depth) {
-                    drain_row<T, ACT, BIAS>(taddr, out_pad, layer_bias, [&](int chunk, uint4 packed) {
-                        st_shared_16(row_addr + ((chunk << 4) ^ row_swizzle), packed);
-                    });
-                    fence_async_smem();
+                    if constexpr (TA) {
+                        drain_row<T, ACT, BIAS>(taddr, out_pad, layer_bias, [&](int chunk, uint4 packed) { tmem_st4(act_taddr + 4 * chunk, packed); });
+                        tmem_st_wait();
+                    } else {
+                        drain_row<T, ACT, BIAS>(taddr, out_pad, layer_bias, [&](int chunk, uint4 packed) {
+                            st_shared_16(row_addr + ((chunk << 4) ^ row_swizzle), packed);
+                        });
+                        fence_async_smem();
+                    }
                 } else {
                     const bool live = row0 + row < n_rows;
                     if constexpr (MSE) {
@@ -1217,7 +1230,15 @@ bool pipe_disabled() {
     return off;
 }
 
-template <typename T, int ACT, bool BIAS, int S, bool MSE = false>
+bool tmem_a_enabled() {
+    static const bool on = [] {
+        const char *v = getenv("TH_MLP_NO_TMEM_A");
+        return !(v && v[0] == '1');
+    }();
+    return on;
+}
+
+template <typename T, int ACT, bool BIAS, int S, bool MSE, bool TA>
 int launch_fwd_pipe(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, void *y, int64_t y_stride,
                     int64_t rows, cudaStream_t stream, const MseArgs &mse = MseArgs{}) {
     const TcPlan P = tc_plan(s, false, 2 * S);
@@ -1228,7 +1249,8 @@ int launch_fwd_pipe(const MlpShape &s, const MlpParams &p, const void *x, int64_
     CUtensorMap x_map;
     if (!make_weight_maps(maps, s, p)) return kTcNotApplicable;
     if (!make_map(&x_map, x, rows, s.d_in, kTileRows, x_stride)) return kTcNotApplicable;
-    auto kernel = mlp_fwd_pipe_kernel<T, ACT, BIAS, S, MSE>;
+    if (S * (kAccCols + (TA ? 32 : 0)) > 512) return kTcNotApplicable;
+    auto kernel = mlp_fwd_pipe_kernel<T, ACT, BIAS, S, MSE, TA>;
     if (int rc = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
                              "cudaFuncSetAttribute(mlp_fwd_pipe_kernel)")) return rc;
     const long long tiles = (rows + kTileRows - 1) / kTileRows;
@@ -1238,20 +1260,28 @@ int launch_fwd_pipe(const MlpShape &s, const MlpParams &p, const void *x, int64_
     return launch_status("mlp_fwd_pipe_kernel launch");
 }
 
-// Four slots measured best (2^21 rows, 32-64-64-16: 3 slots 0.136 ms, 4: 0.103, 5: 0.116, 6: 0.126; the
-// one-tile-per-CTA kernel: 0.193): MMA operand reads and epilogue stores share the SM's shared-memory
-// bandwidth, and beyond four tiles in flight they only queue up behind each other.  Fewer are used
-// (three) when the weights leave less room; TH_MLP_SLOTS=3 or 0 lowers the cap (0 = never).
+// Slots per CTA, measured (2^21 rows, 32-64-64-16, with the loss; 2^20 rows, 32-4x64-16):
+//   activations through shared memory: 3 slots 0.136 ms, 4: 0.122 / 0.083, 5: 0.127 / 0.098, 6: 0.153 - MMA operand reads and
+//     epilogue stores share the SM's shared-memory bandwidth, and beyond four tiles in flight they only queue up;
+//   activations through tensor memory: 3 slots 0.128 / 0.088, 4: 0.104 / 0.069, 5: 0.092 / 0.064 - five slots x 96 columns are
+//     what tensor memory holds.
+// TH_MLP_SLOTS=n lowers the cap (0 = never), TH_MLP_NO_TMEM_A=1 keeps the activations in shared memory.
 template <typename T, int ACT, bool BIAS, bool MSE>
 int launch_fwd_slots(const MlpShape &s, const MlpParams &p, const void *x, int64_t x_stride, void *y, int64_t y_stride,
                      int64_t rows, cudaStream_t stream, const MseArgs &mse) {
     static const int cap = [] {
         const char *v = getenv("TH_MLP_SLOTS");
-        return v ? atoi(v) : 4;
+        return v ? atoi(v) : 5;
     }();
     int rc = kTcNotApplicable;
-    if (cap >= 4) rc = launch_fwd_pipe<T, ACT, BIAS, 4, MSE>(s, p, x, x_stride, y, y_stride, rows, stream, mse);
-    if (rc == kTcNotApplicable && cap >= 3) rc = launch_fwd_pipe<T, ACT, BIAS, 3, MSE>(s, p, x, x_stride, y, y_stride, rows, stream, mse);
+    if (tmem_a_enabled()) {
+        if (cap >= 5) rc = launch_fwd_pipe<T, ACT, BIAS, 5, MSE, true>(s, p, x, x_stride, y, y_stride, rows, stream, mse);
+        if (rc == kTcNotApplicable && cap >= 4) rc = launch_fwd_pipe<T, ACT, BIAS, 4, MSE, true>(s, p, x, x_stride, y, y_stride, rows, stream, mse);
+        if (rc == kTcNotApplicable && cap >= 3) rc = launch_fwd_pipe<T, ACT, BIAS, 3, MSE, true>(s, p, x, x_stride, y, y_stride, rows, stream, mse);
+        return rc;
+    }
+    if (cap >= 4) rc = launch_fwd_pipe<T, ACT, BIAS, 4, MSE, false>(s, p, x, x_stride, y, y_stride, rows, stream, mse);
+    if (rc == kTcNotApplicable && cap >= 3) rc = launch_fwd_pipe<T, ACT, BIAS, 3, MSE, false>(s, p, x, x_stride, y, y_stride, rows, stream, mse);
     return rc;
 }
 

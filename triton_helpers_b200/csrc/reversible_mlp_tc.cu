@@ -40,6 +40,7 @@ constexpr int kStageBytes = 4 * kWTileBytes;     // [f1 | f2 | g1 | g2]
 // TMEM columns
 constexpr int kS1 = 0, kS2 = 64;                 // the stream
 constexpr int kFwdHid = 128;                     // forward: hidden pre-activation
+constexpr int kFwdAU = 192, kFwdAH = 224;        // forward: 16-bit A operands (the branch's input, its hidden activation), 32 columns each
 constexpr int kD1 = 128, kD2 = 192, kZ = 256, kDH = 320, kDW1 = 384, kDW2 = 448;  // backward
 
 struct RevTcPlan {
@@ -167,6 +168,27 @@ __device__ __forceinline__ void stream_epilogue(uint32_t taddr, const Seat &seat
     if constexpr (BIAS) tmem_st_wait();
 }
 
+// The same with the rounded copy going to a 16-bit A operand in tensor memory (4 columns per 16-byte chunk).
+template <typename T, bool BIAS>
+__device__ __forceinline__ void stream_epilogue_ta(uint32_t taddr, const Seat &seat, int width, const float *bias, uint32_t a_taddr,
+                                                   T *global_row, bool live) {
+    const int n = width / kGroups, first = seat.group * (n / 8);
+    for_each_piece(taddr + seat.group * n, n, [&](int u, const uint32_t(&piece)[8]) {
+        uint32_t v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = piece[k];
+        if constexpr (BIAS) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = __float_as_uint(__uint_as_float(v[k]) + bias[8 * (first + u) + k]);
+            tmem_st8(taddr + 8 * (first + u), v);
+        }
+        const uint4 packed = finish8<T, TH_ACT_NONE, false>(v, nullptr);
+        tmem_st4(a_taddr + 4 * (first + u), packed);
+        if (global_row && live) __stcs(reinterpret_cast<uint4 *>(global_row + 8 * (first + u)), packed);
+    });
+    tmem_st_wait();
+}
+
 __device__ __forceinline__ bool commit_and_wait(bool leader, uint32_t bar, uint32_t &phase, int *abort_flag) {
     if (threadIdx.x < 32) {
         if (leader) mma_commit(bar);
@@ -183,7 +205,9 @@ __device__ __forceinline__ void publish_tiles() {
 
 // ---- forward -----------------------------------------------------------------------------------
 
-template <typename T, int ACT, bool BIAS>
+// TA: the two A operands of a branch (the 16-bit copy of its input stream, its hidden activation) live in tensor
+// memory and never touch shared memory; the operand tiles only stage the rows as they arrive.
+template <typename T, int ACT, bool BIAS, bool TA>
 __global__ void __launch_bounds__(kTcThreads, 2)
 rev_fwd_tc_kernel(const RevShape s, const RevParams p, const __grid_constant__ RevWeightMaps maps, const int use_tma,
                   const T *__restrict__ x, long long x_stride, T *__restrict__ y, long long y_stride, long long n_rows) {
@@ -227,6 +251,11 @@ rev_fwd_tc_kernel(const RevShape s, const RevParams p, const __grid_constant__ R
         __syncthreads();
         tile_row_to_tmem<T>(h_tile, seat, s.half, taddr + kS1);
         tile_row_to_tmem<T>(u_tile, seat, s.half, taddr + kS2);
+        if constexpr (TA) {  // x2 as the first branch's A operand
+            const int count = s.half / (8 * kGroups), first = seat.group * count;
+            for (int u = 0; u < count; ++u)
+                tmem_st4(taddr + kFwdAU + 4 * (first + u), *reinterpret_cast<const uint4 *>(chunk_ptr(u_tile, seat.row, first + u)));
+        }
         tmem_st_wait();
         publish_tiles();
 
@@ -249,7 +278,8 @@ rev_fwd_tc_kernel(const RevShape s, const RevParams p, const __grid_constant__ R
                 if (threadIdx.x < 32) {
                     leader = elect_one();
                     tc_fence_after();
-                    issue_gemm(leader, tmem + kFwdHid, smem_addr(u_tile), 32, w1, 32, s.half / 16, idesc_hid, false);
+                    if constexpr (TA) issue_gemm_ta(leader, tmem + kFwdHid, tmem + kFwdAU, w1, 32, s.half / 16, idesc_hid, false);
+                    else issue_gemm(leader, tmem + kFwdHid, smem_addr(u_tile), 32, w1, 32, s.half / 16, idesc_hid, false);
                 }
                 commit_and_wait(leader, bar, phase, &abort_flag);
                 {
@@ -257,20 +287,28 @@ rev_fwd_tc_kernel(const RevShape s, const RevParams p, const __grid_constant__ R
                     const uint32_t row_addr = smem_addr(h_tile) + seat.row * 128, row_swizzle = (seat.row & 7) << 4;
                     const float *layer_bias = bias + (2 * branch) * kMaxDim;
                     for_each_piece(taddr + kFwdHid + seat.group * n, n, [&](int u, const uint32_t(&piece)[8]) {
-                        st_shared_16(row_addr + (((first + u) << 4) ^ row_swizzle), finish8<T, ACT, BIAS>(piece, layer_bias + 8 * (first + u)));
+                        const uint4 packed = finish8<T, ACT, BIAS>(piece, layer_bias + 8 * (first + u));
+                        if constexpr (TA) tmem_st4(taddr + kFwdAH + 4 * (first + u), packed);
+                        else st_shared_16(row_addr + (((first + u) << 4) ^ row_swizzle), packed);
                     });
+                    if constexpr (TA) tmem_st_wait();
                 }
                 publish_tiles();
                 if (threadIdx.x < 32) {
                     leader = elect_one();
                     tc_fence_after();
-                    issue_gemm(leader, tmem + out_col, smem_addr(h_tile), 32, w2, 32, s.hid / 16, idesc_half, true);
+                    if constexpr (TA) issue_gemm_ta(leader, tmem + out_col, tmem + kFwdAH, w2, 32, s.hid / 16, idesc_half, true);
+                    else issue_gemm(leader, tmem + out_col, smem_addr(h_tile), 32, w2, 32, s.hid / 16, idesc_half, true);
                 }
                 commit_and_wait(leader, bar, phase, &abort_flag);
                 // the updated stream: rounded copy for the next branch, and the output after the last block
                 const bool last = k == s.blocks - 1;
-                stream_epilogue<T, BIAS>(taddr + out_col, seat, s.half, bias + (2 * branch + 1) * kMaxDim, u_tile,
-                                         last ? y_row + branch * s.half : nullptr, live);
+                if constexpr (TA)
+                    stream_epilogue_ta<T, BIAS>(taddr + out_col, seat, s.half, bias + (2 * branch + 1) * kMaxDim, taddr + kFwdAU,
+                                                last ? y_row + branch * s.half : nullptr, live);
+                else
+                    stream_epilogue<T, BIAS>(taddr + out_col, seat, s.half, bias + (2 * branch + 1) * kMaxDim, u_tile,
+                                             last ? y_row + branch * s.half : nullptr, live);
                 if (branch == 1) {  // next block's weights have landed
                     if (!use_tma) async_tile_wait();
                     else if (more) ring_wait(ring_bars, step + 1, &abort_flag);
@@ -612,13 +650,22 @@ int make_rev_maps(RevWeightMaps &maps, const RevShape &s, const RevParams &p) {
     return 1;
 }
 
-template <typename T, int ACT, bool BIAS>
-int launch_rev_fwd_t(const RevShape &s, const RevParams &p, const void *x, int64_t x_stride, void *y, int64_t y_stride,
-                     int64_t rows, cudaStream_t stream) {
+// TH_MLP_NO_TMEM_A=1 keeps the A operands of the forward GEMMs in shared memory (for A/B runs).
+bool rev_tmem_a_enabled() {
+    static const bool on = [] {
+        const char *v = getenv("TH_MLP_NO_TMEM_A");
+        return !(v && v[0] == '1');
+    }();
+    return on;
+}
+
+template <typename T, int ACT, bool BIAS, bool TA>
+int launch_rev_fwd_ta(const RevShape &s, const RevParams &p, const void *x, int64_t x_stride, void *y, int64_t y_stride,
+                      int64_t rows, cudaStream_t stream) {
     const RevTcPlan P = rev_tc_plan(false);
     const int ctas = 2;  // 256 of the 512 TMEM columns each
     const int smem = smem_request(P, ctas);
-    auto kernel = rev_fwd_tc_kernel<T, ACT, BIAS>;
+    auto kernel = rev_fwd_tc_kernel<T, ACT, BIAS, TA>;
     if (int rc = cuda_status(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
                              "cudaFuncSetAttribute(rev_fwd_tc_kernel)")) return rc;
     const long long tiles = (rows + kTileRows - 1) / kTileRows;
@@ -628,6 +675,13 @@ int launch_rev_fwd_t(const RevShape &s, const RevParams &p, const void *x, int64
     kernel<<<static_cast<unsigned>(tiles < cap ? tiles : cap), kTcThreads, smem, stream>>>(
         s, p, maps, use_tma, static_cast<const T *>(x), x_stride, static_cast<T *>(y), y_stride, rows);
     return launch_status("rev_fwd_tc_kernel launch");
+}
+
+template <typename T, int ACT, bool BIAS>
+int launch_rev_fwd_t(const RevShape &s, const RevParams &p, const void *x, int64_t x_stride, void *y, int64_t y_stride,
+                     int64_t rows, cudaStream_t stream) {
+    return rev_tmem_a_enabled() ? launch_rev_fwd_ta<T, ACT, BIAS, true>(s, p, x, x_stride, y, y_stride, rows, stream)
+                                : launch_rev_fwd_ta<T, ACT, BIAS, false>(s, p, x, x_stride, y, y_stride, rows, stream);
 }
 
 template <typename T, bool BIAS>

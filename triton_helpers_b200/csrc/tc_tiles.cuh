@@ -468,6 +468,29 @@ __device__ __forceinline__ void issue_gemm(bool leader, uint32_t tmem_d, uint32_
     }
 }
 
+// A-operand in tensor memory: [d] += [a_tmem] * b(smem).  Row i of A sits in lane i, two consecutive K elements per
+// 32-bit column, so a 16-deep K step is 8 columns.
+__device__ __forceinline__ void mma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void issue_gemm_ta(bool leader, uint32_t tmem_d, uint32_t tmem_a, uint32_t b_addr, uint32_t b_step, int k_steps,
+                                              uint32_t idesc, bool accumulate) {
+    uint32_t b_low = desc_low(b_addr);
+    for (int k = 0; k < k_steps; ++k) {
+        if (leader) mma_f16_ta(tmem_d, tmem_a + 8 * k, smem_desc(b_low), idesc, (accumulate || k > 0) ? 1u : 0u);
+        b_low += b_step >> 4;
+    }
+}
+
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, uint4 v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
 // Which rows / columns a thread looks after: TMEM lanes 32 * (warp % 4) .. + 31, column half warp / 4.
 struct Seat {
     int row;            // tile row = TMEM lane
