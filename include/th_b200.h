@@ -24,7 +24,8 @@
  *     mma.sync kernels, TH_MLP_NO_TMA=1 stages weights with plain loads, TH_MLP_NO_PIPE=1
  *     disables the multi-tile tcgen05 MLP kernels, TH_MLP_NO_SLOTS=1 only the backward's
  *     shared-accumulator variant of them, TH_MLP_SLOTS=n caps the forward's row tiles in
- *     flight per CTA.
+ *     flight per CTA, TH_MLP_NO_TMEM_A=1 keeps the forward kernels' hidden activations in
+ *     shared-memory operand tiles instead of tensor memory.
  *
  * dtype codes: TH_F32 = 0, TH_F16 = 1, TH_BF16 = 2.
  * activation codes: TH_ACT_NONE = 0, TH_ACT_RELU = 1, TH_ACT_SILU = 2, TH_ACT_RELU2 = 3
