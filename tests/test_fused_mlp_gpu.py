@@ -424,6 +424,22 @@ def test_pipelined_backward_still_passes_when_the_shared_accumulator_kernel_is_o
     assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-2000:]
 
 
+def test_forward_through_shared_memory_still_passes_when_selected():
+    # TH_MLP_NO_TMEM_A=1 keeps the forward kernels' hidden activations in shared-memory operand tiles (the form the
+    # tensor-memory A operand replaced); rerun the forward and shape tests that way in a fresh process
+    import os
+    import subprocess
+    import sys
+
+    if os.environ.get("TH_MLP_NO_TMEM_A") == "1" or os.environ.get("TH_MLP_LEGACY") == "1":
+        pytest.skip("already running without the tensor-memory A operand")
+    env = dict(os.environ, TH_MLP_NO_TMEM_A="1")
+    cmd = [sys.executable, "-m", "pytest", __file__, "-q", "-x", "-m", "gpu", "-k",
+           "forward_reference_shapes or shapes_against_oracle or row_count_edges or forward_fused_with_mse"]  # fmt: skip
+    done = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-2000:]
+
+
 # ---- forward fused with the squared-error loss -----------------------------------------------------
 
 

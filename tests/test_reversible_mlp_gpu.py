@@ -227,3 +227,17 @@ def test_mma_sync_kernels_still_pass_when_selected():
     cmd = [sys.executable, "-m", "pytest", __file__, "-q", "-x", "-m", "gpu", "-k", "against_oracle or float32_autograd"]
     done = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
     assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-2000:]
+
+
+def test_forward_through_shared_memory_still_passes_when_selected():
+    # TH_MLP_NO_TMEM_A=1 keeps the forward kernel's A operands in shared-memory operand tiles instead of tensor memory
+    import os
+    import subprocess
+    import sys
+
+    if os.environ.get("TH_MLP_NO_TMEM_A") == "1" or os.environ.get("TH_MLP_LEGACY") == "1":
+        pytest.skip("already running without the tensor-memory A operand")
+    env = dict(os.environ, TH_MLP_NO_TMEM_A="1")
+    cmd = [sys.executable, "-m", "pytest", __file__, "-q", "-x", "-m", "gpu", "-k", "against_oracle or float32_autograd"]
+    done = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-2000:]
