@@ -424,6 +424,32 @@ def test_pipelined_backward_still_passes_when_the_shared_accumulator_kernel_is_o
     assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-2000:]
 
 
+def test_float32_tensors_with_bfloat16_operands_keep_the_range():
+    # float32 tensors are rounded to float16 operands (TF32's mantissa); values beyond 65 504 then overflow.
+    # TH_MLP_F32_OPERANDS=bf16 (read once per process, hence the child process) trades mantissa for TF32's range.
+    import os
+    import subprocess
+    import sys
+
+    code = """
+import torch
+from oracle import fused_mlp as oracle
+from triton_helpers_b200.layers.fully_fused_mlp import fully_fused_mlp
+g = torch.Generator().manual_seed(0)
+x = torch.randn(1, 300, 8, generator=g) * 3e5
+w_in, w_out = torch.randn(16, 8, generator=g) * 0.3, torch.randn(4, 16, generator=g) * 0.3
+want = oracle.forward(x, w_in, None, w_out, None, None, None)
+got = fully_fused_mlp(x.cuda(), w_in.cuda(), None, w_out.cuda(), None, None, None)
+assert got.dtype == torch.float32 and torch.isfinite(got).all(), got
+err = float((got.cpu() - want).abs().max() / want.abs().max())
+assert err <= 3e-2, err
+"""
+    env = dict(os.environ, TH_MLP_F32_OPERANDS="bf16")
+    done = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600,
+                          cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert done.returncode == 0, done.stdout[-2000:] + done.stderr[-3000:]
+
+
 def test_forward_through_shared_memory_still_passes_when_selected():
     # TH_MLP_NO_TMEM_A=1 keeps the forward kernels' hidden activations in shared-memory operand tiles (the form the
     # tensor-memory A operand replaced); rerun the forward and shape tests that way in a fresh process

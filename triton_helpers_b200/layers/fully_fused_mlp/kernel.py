@@ -10,8 +10,10 @@ Differences a caller can observe:
 * float32 tensors are accepted like in the reference, whose ``tl.dot`` then runs in TF32 (10-bit
   operand mantissa, float32 accumulation).  Here they are rounded to float16 (the same 10-bit
   mantissa, float32 accumulation) for the tensor cores and the results are returned in float32;
-  values beyond the float16 range (|v| > 65504) overflow, which TF32 would not.  As in the
-  reference, a float32 backward pass is refused for depth >= 4 (reference :576).
+  values beyond the float16 range (|v| > 65504) overflow, which TF32 would not.  Setting the
+  environment variable ``TH_MLP_F32_OPERANDS=bf16`` before the first call rounds float32 tensors to
+  bfloat16 instead (TF32's exponent range, 8 instead of 10 mantissa bits) for data that needs the range.
+  As in the reference, a float32 backward pass is refused for depth >= 4 (reference :576).
 * ``fp16_acc=True`` is accepted (the reference's callers and benchmarks pass it) but changes nothing:
   accumulation is always float32, which is at least as accurate as what was asked for.  The first
   such call emits a ``UserWarning`` saying so.
@@ -31,6 +33,23 @@ from ...ops import ensure_str
 # Above this size the weights no longer stay on chip (reference :13-14)
 FULLY_FUSED_MAX_DIM: Final = 64
 ACTIVATIONS: Final = ("relu", "relu2", "silu", "none")
+
+
+_F32_OPERANDS: Optional[torch.dtype] = None
+
+
+def _f32_operand_dtype() -> torch.dtype:
+    r"""The 16-bit type float32 tensors are rounded to for the tensor cores: float16 (TF32's mantissa) unless
+    ``TH_MLP_F32_OPERANDS=bf16`` asks for bfloat16 (TF32's range).  Read once per process."""
+    global _F32_OPERANDS
+    if _F32_OPERANDS is None:
+        import os
+
+        choice = os.environ.get("TH_MLP_F32_OPERANDS", "fp16").lower()
+        if choice not in ("fp16", "float16", "bf16", "bfloat16"):
+            raise ValueError(f"TH_MLP_F32_OPERANDS must be fp16 or bf16, got {choice!r}")
+        _F32_OPERANDS = torch.bfloat16 if choice.startswith("b") else torch.float16
+    return _F32_OPERANDS
 
 
 _FP16_ACC_WARNED = False
@@ -108,7 +127,7 @@ class _fully_fused_mlp(Function):
 
         device = _lib.require_cuda(x, w_in, b_in, w_out, b_out, w_hid, b_hid)
         io_dtype = _check_dtype(x, w_in, b_in, w_out, b_out, w_hid, b_hid)
-        dtype = torch.float16 if io_dtype == torch.float32 else io_dtype  # float32: float16 operands, fp32 accumulate
+        dtype = _f32_operand_dtype() if io_dtype == torch.float32 else io_dtype  # float32: 16-bit operands, fp32 accumulate
         if io_dtype == torch.float32:
             x, w_in, w_out = x.to(dtype), w_in.to(dtype), w_out.to(dtype)
             w_hid = None if w_hid is None else w_hid.to(dtype)
