@@ -75,6 +75,7 @@ hash_fwd_kernel(const __grid_constant__ LevelParams P, const CoordView cv, const
             const T *base = table + P.offset[level] * F;
             // (loads that skip L1 allocation were tried for the hashed levels and measured slower:
             //  0.60 against 0.55 ms at 2^21 points, 3.5 against 2.2 ms with a 681 MB table)
+            // (and an evict-last hint on the small dense levels changed nothing: 0.557 against 0.552 ms)
 #pragma unroll
             for (int c = 0; c < kSide; ++c) load_elems<T, F, 0>(base + static_cast<size_t>(idx[c]) * F, e[j][c]);
         }
