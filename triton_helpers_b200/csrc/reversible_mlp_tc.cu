@@ -377,6 +377,10 @@ __device__ __forceinline__ void flush_dw_quadrant(uint32_t tmem, int q, uint32_t
     const int m = 16 * q + lane;
     const bool owner = lane < 16 && m < out_dim;
     const uint32_t taddr = tmem + (static_cast<uint32_t>(32 * q) << 16) + col;
+    // The private copies (0.5 MB per CTA) are revisited once per row tile while a gigabyte of rows streams through
+    // L2: ask the L2 to keep their lines (evict-last), or most of the reductions end up in DRAM.
+    unsigned long long keep;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(keep));
     for (int first = 0; first < in_dim; first += 16) {
         uint32_t raw[32];
         tmem_ld16(taddr + first, raw);
@@ -384,9 +388,9 @@ __device__ __forceinline__ void flush_dw_quadrant(uint32_t tmem, int q, uint32_t
         if (owner) {
 #pragma unroll
             for (int h = 0; h < 4; ++h)
-                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + dw_private_index(m, first + 4 * h)),
+                asm volatile("red.global.add.L2::cache_hint.v4.f32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(dst + dw_private_index(m, first + 4 * h)),
                              "f"(__uint_as_float(raw[4 * h])), "f"(__uint_as_float(raw[4 * h + 1])),
-                             "f"(__uint_as_float(raw[4 * h + 2])), "f"(__uint_as_float(raw[4 * h + 3]))
+                             "f"(__uint_as_float(raw[4 * h + 2])), "f"(__uint_as_float(raw[4 * h + 3])), "l"(keep)
                              : "memory");
         }
     }
